@@ -1,0 +1,97 @@
+"""ctypes binding of librf_b200.so (the C ABI declared in include/rf_b200.h).
+
+There is no fallback: if the shared library is missing or a symbol cannot be
+resolved, importing the binding raises.
+"""
+import ctypes
+import os
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "librf_b200.so")
+
+RF_OK = 0
+STATUS_NAMES = {
+    0: "RF_OK", 1: "RF_ERR_BAD_SHAPE", 2: "RF_ERR_NULL_POINTER", 3: "RF_ERR_MISALIGNED", 4: "RF_ERR_WORKSPACE",
+    5: "RF_ERR_CUDA", 6: "RF_ERR_DEVICE_TIMEOUT", 7: "RF_ERR_UNSUPPORTED", 8: "RF_ERR_COMM",
+}
+
+
+class RfError(RuntimeError):
+    def __init__(self, what: str, status: int):
+        super().__init__(f"{what}: {STATUS_NAMES.get(status, status)}")
+        self.status = status
+
+
+class PerfMetricEntry(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char * 20), ("time", ctypes.c_float), ("gflops", ctypes.c_float)]
+
+
+class PerfMetrics(ctypes.Structure):
+    _fields_ = [("count", ctypes.c_int), ("entries", PerfMetricEntry * 20)]
+
+
+class InputParams(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "batch_size", "seq_len", "d_hidden", "d_expert", "n_routed_experts", "n_experts_per_token",
+        "n_shared_experts", "seed")]
+
+
+_MOE_PTR_FIELDS = (
+    "expert_weight_gate_transposed", "expert_weight_up_transposed", "expert_weight_down_transposed",
+    "input_seq",
+    "shared_expert_weight_gate", "shared_expert_weight_gate_transposed",
+    "shared_expert_weight_up", "shared_expert_weight_up_transposed",
+    "shared_expert_weight_down", "shared_expert_weight_down_transposed",
+    "router_weight", "expert_scores", "seq_experts_index", "seq_experts_softmax", "source_rows",
+    "permuted_experts", "permuted_rows", "first_token_offset", "expanded_seq_input", "expanded_seq_softmax",
+    "rev_permuted_rows", "expanded_fc1_output", "expanded_fc1_gate_splitk", "expanded_fc1_up_splitk",
+    "expanded_fc2_output", "expanded_fc2_splitk", "shared_fc1_output", "shared_fc1_gate_splitk",
+    "shared_fc1_up_splitk", "shared_fc2_output", "shared_fc2_splitk", "final_output", "final_output_splitk",
+)
+
+
+class MoEInputRaw(ctypes.Structure):
+    _fields_ = (
+        [("params", InputParams),
+         ("expert_weight_gate", ctypes.POINTER(ctypes.c_void_p)),
+         ("expert_weight_up", ctypes.POINTER(ctypes.c_void_p)),
+         ("expert_weight_down", ctypes.POINTER(ctypes.c_void_p))]
+        + [(n, ctypes.c_void_p) for n in _MOE_PTR_FIELDS]
+    )
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing - build it with `python -m radeonflow_kernels_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        _lib = ctypes.CDLL(LIB_PATH)
+        _declare(_lib)
+    return _lib
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    L.rf_version.restype = ctypes.c_char_p
+    L.rf_version.argtypes = []
+    L.rf_device_status.restype = ci
+    L.rf_device_status.argtypes = [ctypes.POINTER(ci)]
+    L.run.restype = None
+    L.run.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ctypes.POINTER(PerfMetrics), vp]
+    L.rf_fp8_gemm.restype = ci
+    L.rf_fp8_gemm.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, sz, vp]
+    L.rf_fp8_gemm_workspace_bytes.restype = sz
+    L.rf_fp8_gemm_workspace_bytes.argtypes = [ci, ci, ci, ci]
+    L.rf_fp8_gemm_choose_split.restype = ci
+    L.rf_fp8_gemm_choose_split.argtypes = [ci, ci, ci]
+
+
+def check(status: int, what: str) -> None:
+    if status != RF_OK:
+        raise RfError(what, status)

@@ -1,0 +1,167 @@
+// C-ABI entry points of the FP8 block-scaled GEMM (declared in include/rf_b200.h).
+#include "../../include/rf_b200.h"
+#include "fp8_gemm.h"
+#include "host_util.h"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+namespace {
+
+constexpr int kBlockK = 128;
+
+bool shape_ok(int m, int n, int k) { return m > 0 && n > 0 && k > 0 && (n % 64) == 0 && (k % kBlockK) == 0; }
+
+// Split-K choice: minimise (waves) x (K blocks per slice + per-tile fixed cost)
+// plus the cost of the fp32 slice round trip through HBM.  Units: one 128-deep
+// K block of one 128 x BN tile (about 0.14 us at full tensor rate).
+int choose_split(int m, int n, int k, int num_sms) {
+    const int bn = rf::fp8_gemm_block_n();
+    const int tiles = ((m + 127) / 128) * ((n + bn - 1) / bn);
+    const int kb = k / kBlockK;
+    if (tiles >= num_sms || kb < 8) return 1;
+    double best_cost = 1e30;
+    int best = 1;
+    for (int s = 1; s <= 8 && kb / s >= 4; ++s) {
+        const int waves = (tiles * s + num_sms - 1) / num_sms;
+        const int kb_per = (kb + s - 1) / s;
+        double cost = (double)waves * (kb_per + 4.0);
+        if (s > 1) {
+            // slices written + read back once: 8 B per element per slice at ~6 TB/s,
+            // plus a second kernel launch (~2.5 us)
+            const double bytes = 8.0 * s * (double)m * n + 2.0 * (double)m * n;
+            cost += (bytes / 6.0e12 + 2.5e-6) / 0.14e-6;
+        }
+        if (cost < best_cost) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
+int gemm_impl(const void* a, const void* b, const float* as, const float* bs, void* c, int m, int n, int k,
+              int split_k, void* workspace, size_t workspace_bytes, bool own_workspace, cudaStream_t stream) {
+    if (!shape_ok(m, n, k)) return RF_ERR_BAD_SHAPE;
+    if (!a || !b || !as || !bs || !c) return RF_ERR_NULL_POINTER;
+    if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) return RF_ERR_MISALIGNED;
+    if (((uintptr_t)as | (uintptr_t)bs) & 3) return RF_ERR_MISALIGNED;
+    rf::DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+
+    const int bn = rf::fp8_gemm_block_n();
+    const int kb = k / kBlockK;
+    int splits = split_k > 0 ? split_k : choose_split(m, n, k, st->num_sms);
+    if (splits > kb) splits = kb;
+    if (splits < 1) splits = 1;
+
+    float* partial = nullptr;
+    if (splits > 1) {
+        const size_t need = (size_t)splits * m * n * sizeof(float);
+        if (own_workspace) {
+            partial = static_cast<float*>(rf::device_scratch(need));
+            if (!partial) return RF_ERR_CUDA;
+        } else {
+            if (!workspace || workspace_bytes < need) return RF_ERR_WORKSPACE;
+            if ((uintptr_t)workspace & 15) return RF_ERR_MISALIGNED;
+            partial = static_cast<float*>(workspace);
+        }
+    }
+
+    CUtensorMap ta, tb;
+    if (!rf::encode_tma_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)m, (uint64_t)k, (uint64_t)k, 128, 128,
+                           true))
+        return RF_ERR_CUDA;
+    if (!rf::encode_tma_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k, (uint64_t)k,
+                           (uint32_t)bn, 128, true))
+        return RF_ERR_CUDA;
+
+    rf::GemmParams p;
+    p.a_scale = as;
+    p.b_scale = bs;
+    p.c = static_cast<__nv_bfloat16*>(c);
+    p.partial = partial;
+    p.status = st->status;
+    p.m = m; p.n = n; p.k = k;
+    p.tiles_m = (m + 127) / 128;
+    p.tiles_n = (n + bn - 1) / bn;
+    p.splits = splits;
+    cudaError_t e = rf::fp8_gemm_launch(ta, tb, p, st->num_sms, stream);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "rf_b200: fp8 gemm launch failed: %s\n", cudaGetErrorString(e));
+        return RF_ERR_CUDA;
+    }
+    return RF_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* rf_version(void) { return "rf_b200 0.1 sm_100a"; }
+
+int rf_device_status(int* detail) {
+    rf::DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    int v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return RF_ERR_CUDA;
+    if (cudaMemcpy(&v, st->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return RF_ERR_CUDA;
+    if (detail) *detail = v;
+    if (v != 0) {
+        cudaMemset(st->status, 0, sizeof(int));
+        return RF_ERR_DEVICE_TIMEOUT;
+    }
+    return RF_OK;
+}
+
+int rf_fp8_gemm_choose_split(int m, int n, int k) {
+    if (!shape_ok(m, n, k)) return 0;
+    rf::DeviceState* st = rf::device_state();
+    if (!st) return 0;
+    int s = choose_split(m, n, k, st->num_sms);
+    const int kb = k / kBlockK;
+    return s > kb ? kb : s;
+}
+
+size_t rf_fp8_gemm_workspace_bytes(int m, int n, int k, int split_k) {
+    if (!shape_ok(m, n, k)) return 0;
+    int s = split_k > 0 ? split_k : rf_fp8_gemm_choose_split(m, n, k);
+    const int kb = k / kBlockK;
+    if (s > kb) s = kb;
+    return s > 1 ? (size_t)s * m * n * sizeof(float) : 0;
+}
+
+int rf_fp8_gemm(const void* a, const void* b, const float* as, const float* bs, void* c, int m, int n, int k,
+                int split_k, void* workspace, size_t workspace_bytes, rf_stream_t stream) {
+    return gemm_impl(a, b, as, bs, c, m, n, k, split_k, workspace, workspace_bytes, false,
+                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+void run(void* a, void* b, void* as, void* bs, void* c, int m, int n, int k, PerfMetrics* metrics,
+         rf_stream_t stream) {
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (metrics) {
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        cudaEventRecord(e0, s);
+    }
+    int rc = gemm_impl(a, b, static_cast<const float*>(as), static_cast<const float*>(bs), c, m, n, k, 0, nullptr, 0,
+                       true, s);
+    if (rc != RF_OK) {
+        fprintf(stderr, "Error: fp8 gemm failed (status %d) for M=%d, K=%d, N=%d\n", rc, m, k, n);
+        abort();
+    }
+    if (metrics) {
+        cudaEventRecord(e1, s);
+        cudaEventSynchronize(e1);
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (metrics->count < 1) metrics->count = 1;
+        strncpy(metrics->entries[0].name, "gemm", sizeof(metrics->entries[0].name) - 1);
+        metrics->entries[0].time = ms;
+        metrics->entries[0].gflops = ms > 0.f ? (float)(2.0 * m * n * k / (ms * 1e-3) / 1e9) : 0.f;
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,83 @@
+#include "host_util.h"
+
+#include <cudaTypedefs.h>
+#include <cstdio>
+#include <mutex>
+
+namespace rf {
+
+namespace {
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+bool load_encode() {
+    if (g_encode) return true;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return false;
+    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    return true;
+}
+}  // namespace
+
+DeviceState* device_state() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    DeviceState* st = &g_dev[dev];
+    if (st->init) return st;
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (st->init) return st;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return nullptr;
+    if (prop.major != 10) {
+        fprintf(stderr, "rf_b200: device %d is sm_%d%d; this library contains sm_100a code only\n", dev, prop.major,
+                prop.minor);
+        return nullptr;
+    }
+    st->num_sms = prop.multiProcessorCount;
+    if (cudaMalloc(&st->status, sizeof(int)) != cudaSuccess) return nullptr;
+    if (cudaMemset(st->status, 0, sizeof(int)) != cudaSuccess) return nullptr;
+    if (!load_encode()) return nullptr;
+    st->init = true;
+    return st;
+}
+
+void* device_scratch(size_t bytes) {
+    DeviceState* st = device_state();
+    if (!st) return nullptr;
+    if (bytes <= st->scratch_bytes) return st->scratch;
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (bytes <= st->scratch_bytes) return st->scratch;
+    // Work already queued may still use the old buffer.
+    if (cudaDeviceSynchronize() != cudaSuccess) return nullptr;
+    if (st->scratch) cudaFree(st->scratch);
+    st->scratch = nullptr;
+    st->scratch_bytes = 0;
+    size_t want = bytes + (bytes >> 2);  // 25 % head-room so slowly growing shapes do not thrash
+    if (cudaMalloc(&st->scratch, want) != cudaSuccess) {
+        if (cudaMalloc(&st->scratch, bytes) != cudaSuccess) return nullptr;
+        want = bytes;
+    }
+    st->scratch_bytes = want;
+    return st->scratch;
+}
+
+bool encode_tma_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
+                   uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                   bool swizzle128) {
+    if (!load_encode()) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    (void)elem_bytes;
+    CUresult r = g_encode(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+}  // namespace rf

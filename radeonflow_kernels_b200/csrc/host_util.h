@@ -1,0 +1,37 @@
+// Host-side helpers shared by the C-ABI translation units: per-device state
+// (SM count, status word, growable scratch), tensor-map encoding through the
+// driver entry point (no link-time dependency on libcuda).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace rf {
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+    bool init = false;
+    int num_sms = 0;
+    int* status = nullptr;          // device status word
+    void* scratch = nullptr;        // library-owned scratch (split-K slices, MoE intermediates)
+    size_t scratch_bytes = 0;
+};
+
+// State of the current device; initialises it on first use (allocates the
+// 4-byte status word).  Returns nullptr when a CUDA call fails.
+DeviceState* device_state();
+
+// Library-owned scratch of at least `bytes` on the current device (grows by
+// freeing and re-allocating; synchronises the device when it grows).
+void* device_scratch(size_t bytes);
+
+// 2-D row-major tensor map: `rows` x `cols` elements of `elem_bytes`, row
+// pitch `pitch_bytes`; box = box_rows x box_cols; 128-byte swizzle when
+// `swizzle128`.  dtype is one of CU_TENSOR_MAP_DATA_TYPE_*.
+bool encode_tma_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
+                   uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                   bool swizzle128);
+
+}  // namespace rf
