@@ -1,0 +1,394 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 block-scaled GEMM hot path (and, as extra keys, the MoE layer).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one pass over the 18-shape benchmark sweep (M in {1024, 6144} x 9 (N,K) pairs, the
+shape list of the reference's benchmark set).  `value` is total algorithmic FLOPs of a step divided
+by the device time of a step, inputs resident in HBM.  `e2e` is the same sweep through the
+`run` C-ABI entry with HOST operands: pinned host -> device copies of A, B and the scales and the
+device -> host copy of C are inside the timed region.
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same sweep on its own GPU
+(independent GEMMs: replicas only, weak scaling, no data-path collective); the step time is the
+max over ranks.
+
+`--impl reference` times the CPU restatement of the reference's PyTorch oracle on the host cores
+on a bounded sample of the same sweep.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+NK_PAIRS = [(1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
+            (512, 7168), (4096, 512)]
+SWEEP = [(m, n, k) for m in (1024, 6144) for (n, k) in NK_PAIRS]
+CPU_SAMPLE = [(1024, n, k) for (n, k) in NK_PAIRS]      # the M=1024 half: ~190 GFLOP per pass
+METRIC = "fp8_blockscaled_gemm_tflops"
+UNIT = "TFLOP/s"
+
+
+def gemm_flops(m, n, k):
+    return 2.0 * m * n * k
+
+
+def gemm_bytes(m, n, k):
+    """Algorithmic HBM bytes: fp8 operands and fp32 scales read once, bf16 C written once."""
+    kb = k // 128
+    nb = (n + 127) // 128
+    return m * k + n * k + 4 * m * kb + 4 * nb * kb + 2 * m * n
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            p = json.load(open(path))
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clocks sampling --
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (read-only)."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+        self._thread.start()
+
+    def _loop(self):
+        names = {
+            0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+            0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting",
+        }
+        while not self._stop.is_set():
+            if self._nvml is not None:
+                try:
+                    n = self._nvml
+                    self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+                    try:
+                        r = n.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                    except Exception:
+                        r = n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                    for bit, name in names.items():
+                        if r & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+            else:
+                try:
+                    out = subprocess.run(
+                        ["nvidia-smi", "-i", str(self.index), "--query-gpu=clocks.sm,clocks.max.sm,"
+                         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap",
+                         "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                    f = [x.strip() for x in out.strip().split(",")]
+                    self.samples.append(int(f[0]))
+                    self.max_mhz = int(f[1])
+                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                       f[2:6]):
+                        if v.lower().startswith("active"):
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+            self._stop.wait(0.02 if self._nvml is not None else 0.2)
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=5)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# ------------------------------------------------------------------------------- CPU reference --
+def cpu_pass(problems):
+    """One pass of the CPU oracle over `problems`; returns (seconds, flops)."""
+    from oracle import fp8_gemm as o
+    t0 = time.perf_counter()
+    fl = 0.0
+    for (a, b, a_s, b_s) in problems:
+        o.fp8_gemm(a, b, a_s, b_s)
+        fl += gemm_flops(a.shape[0], b.shape[0], a.shape[1])
+    return time.perf_counter() - t0, fl
+
+
+def cpu_threads():
+    try:
+        from threadpoolctl import threadpool_info
+        n = [i.get("num_threads", 1) for i in threadpool_info() if i.get("user_api") == "blas"]
+        if n:
+            return max(n)
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+def cpu_problems():
+    from oracle import fp8_gemm as o
+    return [o.generate_input(m, n, k, 100 + i, "baseline") for i, (m, n, k) in enumerate(CPU_SAMPLE)]
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    probs = cpu_problems()
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_pass(probs[:2])
+    times = []
+    fl = 0.0
+    steps = max(1, args.steps)
+    for _ in range(steps):
+        t, fl = cpu_pass(probs)
+        times.append(t)
+    tsum = sum(times)
+    val = fl * steps / tsum / 1e12
+    cores = cpu_threads()
+    sample = "numpy port of the reference oracle (dequantise, fp32 matmul, bf16) on the 9 M=1024 shapes of the sweep"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": tsum / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (CPU dequantised e4m3)", "data": "synthetic",
+        "config": {"workload": "fp8 block-scaled GEMM 18-shape sweep; CPU arm times its M=1024 half per step",
+                   "shapes": CPU_SAMPLE},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------ GPU arm --
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from oracle import fp8_gemm as o  # input generator + CPU baseline leg only
+    from radeonflow_kernels_b200 import _lib, build
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the GPU arm has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    build.build()
+    L = _lib.lib()
+    stream = torch.cuda.current_stream()
+    sptr = ctypes.c_void_p(stream.cuda_stream)
+
+    # ---- resident operands, one set per shape (the sweep touches ~1 GB per step, > 126 MB L2)
+    rng = np.random.default_rng(1234 + rank)
+    shapes = []
+    for i, (m, n, k) in enumerate(SWEEP):
+        # device-side generation keeps set-up short: random e4m3 bytes with |x| <= 240 drawn from N(0,1)
+        g = torch.Generator(device=dev)
+        g.manual_seed(1000 + i)
+        a = torch.randn((m, k), device=dev, generator=g).clamp_(-240, 240).to(torch.float8_e4m3fn)
+        b = torch.randn((n, k), device=dev, generator=g).clamp_(-240, 240).to(torch.float8_e4m3fn)
+        kb, nb = k // 128, (n + 127) // 128
+        a_s = ((0.5 + 1.5 * torch.rand((m, kb), device=dev, generator=g)) * 2.0 ** -7).float()
+        b_s = ((0.5 + 1.5 * torch.rand((nb, kb), device=dev, generator=g)) * 2.0 ** -7).float()
+        c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        shapes.append({"m": m, "n": n, "k": k, "a": a, "b": b, "as": a_s, "bs": b_s, "c": c})
+    del rng
+
+    def launch(s):
+        L.run(s["a"].data_ptr(), s["b"].data_ptr(), s["as"].data_ptr(), s["bs"].data_ptr(), s["c"].data_ptr(),
+              s["m"], s["n"], s["k"], None, sptr)
+
+    def sweep():
+        for s in shapes:
+            launch(s)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    launches_per_step = 0
+    for s in shapes:
+        sp = L.rf_fp8_gemm_choose_split(s["m"], s["n"], s["k"])
+        s["split"] = sp
+        launches_per_step += 1 + (1 if sp > 1 else 0)
+
+    for _ in range(max(3, args.warmup)):
+        sweep()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        sweep()
+    e1.record(stream)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    step_flops = sum(gemm_flops(*x) for x in SWEEP)
+    value = world * step_flops / (ms_step * 1e-3) / 1e12
+
+    # ---- per-shape table: each shape timed alone, L2 flushed (256 MB write) before every launch
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    peaks = measured_peaks()
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    per_shape = []
+    for s in shapes:
+        ts = []
+        for _ in range(5):
+            flush.zero_()
+            a0 = torch.cuda.Event(enable_timing=True)
+            a1 = torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            launch(s)
+            a1.record(stream)
+            torch.cuda.synchronize()
+            ts.append(a0.elapsed_time(a1) * 1e3)
+        us = statistics.median(ts)
+        fl, by = gemm_flops(s["m"], s["n"], s["k"]), gemm_bytes(s["m"], s["n"], s["k"])
+        per_shape.append({
+            "m": s["m"], "n": s["n"], "k": s["k"], "split_k": s["split"], "us": round(us, 2),
+            "tflops": round(fl / us / 1e6, 1), "frac_fp8_peak": round(fl / us / 1e6 / fp8_peak, 3),
+            "gbs": round(by / us / 1e3, 1), "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 3),
+        })
+    status = ctypes.c_int(0)
+    L.rf_device_status(ctypes.byref(status))
+    if status.value != 0:
+        raise SystemExit(f"bench.py: device status {status.value}: a bounded wait expired; numbers are invalid")
+
+    # ---- end to end through `run` with host operands (pinned), copies inside the timed region
+    host = []
+    h2d = d2h = 0
+    for s in shapes:
+        h = {k2: s[k2].cpu().pin_memory() for k2 in ("a", "b", "as", "bs")}
+        h["c"] = torch.empty(s["c"].shape, dtype=torch.bfloat16).pin_memory()
+        host.append(h)
+        h2d += sum(h[k2].numel() * h[k2].element_size() for k2 in ("a", "b", "as", "bs"))
+        d2h += h["c"].numel() * 2
+
+    def e2e_step():
+        for s, h in zip(shapes, host):
+            for k2 in ("a", "b", "as", "bs"):
+                s[k2].copy_(h[k2], non_blocking=True)
+            launch(s)
+            h["c"].copy_(s["c"], non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    f0 = torch.cuda.Event(enable_timing=True)
+    f1 = torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record(stream)
+    barrier()
+    t2 = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t2.item()) / e2e_steps
+    e2e_val = world * step_flops / (e2e_ms * 1e-3) / 1e12
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            probs = cpu_problems()
+            cpu_pass(probs[:1])
+            tsec, fl = cpu_pass(probs)
+            reps = 1
+            while tsec < 8.0 and reps < 4:
+                t_more, _ = cpu_pass(probs)
+                tsec += t_more
+                reps += 1
+            cpu = {"value": fl * reps / tsec / 1e12, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
+                   "sample": f"{reps} pass(es) of the numpy oracle over the 9 M=1024 shapes of the sweep "
+                             f"({fl / 1e9:.0f} GFLOP per pass, {tsec:.1f} s)"}
+        achieved = step_flops / (ms_step * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8 e4m3 x e4m3 -> f32 (exact f32 block scales), bf16 out",
+            "data": "synthetic",
+            "config": {"workload": "fp8 block-scaled GEMM, 18-shape sweep M in {1024,6144} x 9 (N,K)",
+                       "l2": "inputs larger than L2: one step touches ~1.0 GB; per-shape table flushes L2",
+                       "parallelism": "replicas" if world > 1 else "single"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
+                         "frac": achieved / fp8_peak, "traffic": None,
+                         "peak_source": f"2 x bf16_tflops of {peaks['source']} (fp8 rate = 2 x bf16)",
+                         "kernel": "fp8_gemm_kernel"},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "shapes": per_shape,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

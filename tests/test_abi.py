@@ -1,0 +1,66 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the header declares,
+and rejects bad arguments before touching the GPU."""
+import ctypes
+import os
+import re
+
+from radeonflow_kernels_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    names = []
+    for fn in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        if not fn.endswith(".h"):
+            continue
+        src = open(os.path.join(ROOT, "include", fn)).read()
+        src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+        for m in re.finditer(r"^[A-Za-z_][\w \*]*?[\s\*]([A-Za-z_]\w*)\s*\(", src, flags=re.M):
+            name = m.group(1)
+            if name not in ("defined",):
+                names.append(name)
+    return names
+
+
+def test_header_declares_the_reference_entry_points():
+    names = declared_functions()
+    assert "run" in names and "rf_fp8_gemm" in names
+
+
+def test_every_declared_symbol_is_exported(rf_lib):
+    missing = [n for n in declared_functions() if not hasattr(rf_lib, n)]
+    assert not missing, missing
+
+
+def test_version_string(rf_lib):
+    assert b"sm_100a" in rf_lib.rf_version()
+
+
+def test_perfmetrics_layout_matches_reference():
+    # tests/checker/metrics.h:4-13: char[20] + 2 floats = 28 bytes; int count + 20 entries
+    assert ctypes.sizeof(_lib.PerfMetricEntry) == 28
+    assert ctypes.sizeof(_lib.PerfMetrics) == 4 + 20 * 28
+
+
+def test_bad_arguments_are_rejected_on_the_host(rf_lib):
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.addressof(buf)
+    p16 = (p + 15) & ~15
+    args = lambda m, n, k: (p16, p16, p16, p16, p16, m, n, k, 0, None, 0, None)
+    assert rf_lib.rf_fp8_gemm(*args(128, 100, 128)) == 1      # n % 64 != 0
+    assert rf_lib.rf_fp8_gemm(*args(128, 128, 100)) == 1      # k % 128 != 0
+    assert rf_lib.rf_fp8_gemm(*args(0, 128, 128)) == 1
+    assert rf_lib.rf_fp8_gemm(None, p16, p16, p16, p16, 128, 128, 128, 0, None, 0, None) == 2
+    assert rf_lib.rf_fp8_gemm(p16 + 1, p16, p16, p16, p16, 128, 128, 128, 0, None, 0, None) == 3
+    assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 128, 1024, 4) == 4 * 128 * 128 * 4
+    assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 128, 1024, 1) == 0
+    assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 100, 1024, 4) == 0
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    import pytest
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.lib()

@@ -1,0 +1,74 @@
+"""CPU tests: the numpy GEMM oracle against fixtures made by the reference's own ref_kernel."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from oracle import fp8_gemm as o
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "gemm_*.npz")))
+
+
+def test_golden_files_present():
+    assert len(GOLDEN) >= 4
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_oracle_matches_reference_output(path):
+    z = np.load(path)
+    got = o.fp8_gemm(z["a"], z["b"], z["a_scale"], z["b_scale"])
+    ok, nbad, _ = o.check(got, z["c_bits"], rtol=2e-2, atol=1e-3)
+    assert ok, f"{nbad} elements outside the reference tolerance"
+    # tighter than the tolerance: one bf16 ulp plus the fp32 summation-order noise of two different
+    # BLAS calls (visible only on sums that nearly cancel), and rare
+    g = o.bf16_bits_to_f32(got).astype(np.float64)
+    e = o.bf16_bits_to_f32(z["c_bits"]).astype(np.float64)
+    assert np.all(np.abs(g - e) <= np.abs(e) * 2.0 ** -7 + 1e-6 * np.abs(e).max())
+    assert (got != z["c_bits"]).mean() < 1e-3
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_blockwise_form_matches_reference_output(path):
+    z = np.load(path)
+    got = o.fp8_gemm_blockwise(z["a"], z["b"], z["a_scale"], z["b_scale"])
+    ok, nbad, _ = o.check(got, z["c_bits"], rtol=2e-2, atol=1e-3)
+    assert ok, nbad
+    assert (got != z["c_bits"]).mean() < 1e-2
+
+
+def test_e4m3fn_table_and_encoder():
+    t = o.E4M3FN_TO_F32
+    assert t[0x00] == 0.0 and t[0x7E] == 448.0 and np.isnan(t[0x7F]) and np.isnan(t[0xFF])
+    assert t[0x38] == 1.0 and t[0xB8] == -1.0 and t[0x01] == 2.0 ** -9
+    finite = np.array([b for b in range(256) if (b & 0x7F) != 0x7F and b != 0x80], dtype=np.uint8)
+    assert np.array_equal(o.encode_e4m3fn(t[finite]), finite)
+    # values with |x| <= 240 exist in e4m3fnuz too (bias 8: same set scaled by 1/2, max 240)
+    vals = t[finite]
+    vals = vals[np.abs(vals) <= 240]
+    fnuz = set()
+    for b in range(256):
+        if b == 0x80:
+            continue
+        e, m = (b >> 3) & 0xF, b & 7
+        v = (m / 8.0) * 2.0 ** -7 if e == 0 else (1 + m / 8.0) * 2.0 ** (e - 8)
+        fnuz.add(-v if b & 0x80 else v)
+    assert all(float(v) in fnuz for v in vals)
+
+
+def test_bf16_rounding_is_nearest_even():
+    x = np.array([1.0, 1.00390625, 1.01171875, -2.5, 3.0e-40], dtype=np.float32)
+    bits = o.f32_to_bf16_bits(x)
+    assert bits[0] == 0x3F80
+    assert bits[1] == 0x3F80          # 1 + 2^-8: tie -> even
+    assert bits[2] == 0x3F82          # 1 + 3*2^-8: tie -> even (up)
+    assert o.bf16_bits_to_f32(bits)[3] == -2.5
+
+
+def test_generator_is_seeded_and_clipped():
+    a, b, a_s, b_s = o.generate_input(64, 128, 256, 7)
+    a2, _, _, _ = o.generate_input(64, 128, 256, 7)
+    assert np.array_equal(a, a2)
+    assert np.nanmax(np.abs(o.decode_e4m3fn(a))) <= 240
+    assert a_s.shape == (64, 2) and b_s.shape == (1, 2)
+    assert a_s.min() >= 0.5 * 2 ** -7 and a_s.max() <= 2.0 * 2 ** -7
