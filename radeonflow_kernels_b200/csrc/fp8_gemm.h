@@ -17,11 +17,12 @@ struct GemmParams {
     int tiles_m, tiles_n, splits;
 };
 
-size_t fp8_gemm_smem_bytes();
-int fp8_gemm_block_n();
-
 // Launches the GEMM (and the split-K fix-up when p.splits > 1) on `stream`.
-cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const GemmParams& p, int num_sms,
+// `block_n` is the tile width the tensor map of B and p.tiles_n were built for: 128 or 256.
+// `tma_c` stores bf16 C boxes of 32 rows x 64 columns; `tma_p` (used when p.splits > 1) stores fp32
+// slice boxes of 32 rows x 32 columns into the [splits][m][n] scratch.
+cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
+                            const CUtensorMap& tma_p, const GemmParams& p, int block_n, int num_sms,
                             cudaStream_t stream);
 
 }  // namespace rf

@@ -13,29 +13,56 @@ constexpr int kBlockK = 128;
 
 bool shape_ok(int m, int n, int k) { return m > 0 && n > 0 && k > 0 && (n % 64) == 0 && (k % kBlockK) == 0; }
 
-// Split-K choice: minimise (waves) x (K blocks per slice + per-tile fixed cost)
-// plus the cost of the fp32 slice round trip through HBM.  Units: one 128-deep
-// K block of one 128 x BN tile (about 0.14 us at full tensor rate).
-int choose_split(int m, int n, int k, int num_sms) {
-    const int bn = rf::fp8_gemm_block_n();
+// Tuning knob for experiments: RF_FP8_GEMM_BN=128|256 forces the tile width.
+int forced_block_n() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RF_FP8_GEMM_BN");
+        v = e ? atoi(e) : 0;
+        if (v != 128 && v != 256) v = 0;
+    }
+    return v;
+}
+
+struct GemmPlan {
+    int block_n;
+    int splits;
+    double cost;
+};
+
+// Cost model, in units of one 128-deep K block of a 128 x 128 tile at full tensor rate
+// (about 0.14 us): rounds of tiles over the SMs x (K blocks per slice + fixed per-tile cost),
+// plus, for split-K, the fp32 slice round trip through HBM and the second launch.
+GemmPlan plan_for(int m, int n, int k, int num_sms, int bn, int forced_split) {
     const int tiles = ((m + 127) / 128) * ((n + bn - 1) / bn);
     const int kb = k / kBlockK;
-    if (tiles >= num_sms || kb < 8) return 1;
-    double best_cost = 1e30;
-    int best = 1;
-    for (int s = 1; s <= 8 && kb / s >= 4; ++s) {
-        const int waves = (tiles * s + num_sms - 1) / num_sms;
+    const double tile_w = bn / 128.0;
+    GemmPlan best{bn, 1, 1e30};
+    for (int s = 1; s <= 8; ++s) {
+        if (forced_split > 0 && s != forced_split) continue;
+        if (forced_split <= 0 && s > 1 && (kb / s < 4 || tiles >= num_sms)) break;
+        if (s > kb) break;
+        const int rounds = (tiles * s + num_sms - 1) / num_sms;
         const int kb_per = (kb + s - 1) / s;
-        double cost = (double)waves * (kb_per + 4.0);
+        double cost = (double)rounds * (kb_per * tile_w + 4.0);
         if (s > 1) {
-            // slices written + read back once: 8 B per element per slice at ~6 TB/s,
-            // plus a second kernel launch (~2.5 us)
             const double bytes = 8.0 * s * (double)m * n + 2.0 * (double)m * n;
             cost += (bytes / 6.0e12 + 2.5e-6) / 0.14e-6;
         }
-        if (cost < best_cost) { best_cost = cost; best = s; }
+        if (cost < best.cost) best = GemmPlan{bn, s, cost};
     }
+    if (best.cost > 1e29) best = GemmPlan{bn, forced_split > kb ? kb : (forced_split > 0 ? forced_split : 1), 0};
     return best;
+}
+
+GemmPlan choose_plan(int m, int n, int k, int num_sms, int forced_split) {
+    const int fb = forced_block_n();
+    if (fb) return plan_for(m, n, k, num_sms, fb, forced_split);
+    GemmPlan p128 = plan_for(m, n, k, num_sms, 128, forced_split);
+    GemmPlan p256 = plan_for(m, n, k, num_sms, 256, forced_split);
+    // Wide tiles halve the A traffic and the MMA instruction count per FLOP; prefer them unless
+    // they cost noticeably more rounds (ragged N such as 576, or too few tiles).
+    return p256.cost <= p128.cost * 1.02 ? p256 : p128;
 }
 
 int gemm_impl(const void* a, const void* b, const float* as, const float* bs, void* c, int m, int n, int k,
@@ -47,11 +74,11 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     rf::DeviceState* st = rf::device_state();
     if (!st) return RF_ERR_CUDA;
 
-    const int bn = rf::fp8_gemm_block_n();
     const int kb = k / kBlockK;
-    int splits = split_k > 0 ? split_k : choose_split(m, n, k, st->num_sms);
-    if (splits > kb) splits = kb;
-    if (splits < 1) splits = 1;
+    if (split_k > kb) split_k = kb;
+    const GemmPlan plan = choose_plan(m, n, k, st->num_sms, split_k);
+    const int bn = plan.block_n;
+    const int splits = plan.splits;
 
     float* partial = nullptr;
     if (splits > 1) {
@@ -74,6 +101,18 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
                            (uint32_t)bn, 128, true))
         return RF_ERR_CUDA;
 
+    CUtensorMap tc, tp;
+    if (!rf::encode_tma_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, (uint64_t)m, (uint64_t)n, (uint64_t)n * 2, 32,
+                           64, true))
+        return RF_ERR_CUDA;
+    if (splits > 1) {
+        if (!rf::encode_tma_3d(&tp, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, partial, (uint64_t)n, (uint64_t)m,
+                               (uint64_t)splits, 32, 32, true))
+            return RF_ERR_CUDA;
+    } else {
+        tp = tc;
+    }
+
     rf::GemmParams p;
     p.a_scale = as;
     p.b_scale = bs;
@@ -84,7 +123,7 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     p.tiles_m = (m + 127) / 128;
     p.tiles_n = (n + bn - 1) / bn;
     p.splits = splits;
-    cudaError_t e = rf::fp8_gemm_launch(ta, tb, p, st->num_sms, stream);
+    cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, p, bn, st->num_sms, stream);
     if (e != cudaSuccess) {
         fprintf(stderr, "rf_b200: fp8 gemm launch failed: %s\n", cudaGetErrorString(e));
         return RF_ERR_CUDA;
@@ -116,9 +155,7 @@ int rf_fp8_gemm_choose_split(int m, int n, int k) {
     if (!shape_ok(m, n, k)) return 0;
     rf::DeviceState* st = rf::device_state();
     if (!st) return 0;
-    int s = choose_split(m, n, k, st->num_sms);
-    const int kb = k / kBlockK;
-    return s > kb ? kb : s;
+    return choose_plan(m, n, k, st->num_sms, 0).splits;
 }
 
 size_t rf_fp8_gemm_workspace_bytes(int m, int n, int k, int split_k) {

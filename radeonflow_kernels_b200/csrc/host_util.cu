@@ -80,4 +80,18 @@ bool encode_tma_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_by
     return r == CUDA_SUCCESS;
 }
 
+bool encode_tma_3d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base, uint64_t d0,
+                   uint64_t d1, uint64_t d2, uint32_t b0, uint32_t b1, bool swizzle128) {
+    if (!load_encode()) return false;
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {d0 * elem_bytes, d0 * d1 * elem_bytes};
+    cuuint32_t box[3] = {b0, b1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(map, dtype, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 }  // namespace rf

@@ -34,4 +34,8 @@ bool encode_tma_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_by
                    uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
                    bool swizzle128);
 
+// 3-D tensor map over a dense [d2][d1][d0] array (d0 contiguous); box = {b0, b1, 1}.
+bool encode_tma_3d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base, uint64_t d0,
+                   uint64_t d1, uint64_t d2, uint32_t b0, uint32_t b1, bool swizzle128);
+
 }  // namespace rf
