@@ -86,6 +86,162 @@ int rf_fp8_gemm_choose_split(int m, int n, int k);
  * Reference: none - the reference aborts (include/gpu_libs.h:31-37).          */
 int rf_device_status(int *detail);
 
+/* ------------------------------------------------------------------- MoE -- */
+
+/* src/moe/moe.h:3-12 */
+typedef struct {
+    int batch_size;
+    int seq_len;
+    int d_hidden;
+    int d_expert;
+    int n_routed_experts;
+    int n_experts_per_token;
+    int n_shared_experts;
+    int seed;
+} InputParams;
+
+/* src/moe/moe.h:14-65 - identical field order.  Every pointer is a device
+ * buffer supplied by the caller except expert_weight_{gate,up,down}, which are
+ * HOST arrays of n_routed_experts device pointers (tests/moe/moe_topk_test.cpp:140-152).
+ * The *_transposed and *_splitk fields are accepted and ignored.             */
+typedef struct {
+    InputParams params;
+    void **expert_weight_gate;  /* [E] -> fp16 [d_hidden, d_expert] row-major */
+    void **expert_weight_up;    /* [E] -> fp16 [d_hidden, d_expert]           */
+    void **expert_weight_down;  /* [E] -> fp16 [d_expert, d_hidden]           */
+
+    void *expert_weight_gate_transposed;
+    void *expert_weight_up_transposed;
+    void *expert_weight_down_transposed;
+
+    void *input_seq;            /* fp16 [T, d_hidden], T = batch_size*seq_len */
+
+    void *shared_expert_weight_gate; /* fp16 [d_hidden, d_expert*n_shared]    */
+    void *shared_expert_weight_gate_transposed;
+    void *shared_expert_weight_up;
+    void *shared_expert_weight_up_transposed;
+    void *shared_expert_weight_down; /* fp16 [d_expert*n_shared, d_hidden]    */
+    void *shared_expert_weight_down_transposed;
+
+    void *router_weight;        /* fp16 [E, d_hidden]                         */
+
+    void *expert_scores;        /* fp16 [T, E] router logits (input; see run_topk) */
+
+    void *seq_experts_index;    /* int32 [T, k]                               */
+    void *seq_experts_softmax;  /* fp16  [T, k]                               */
+
+    void *source_rows;          /* int32 [T*k], value = k_idx*T + t           */
+
+    void *permuted_experts;     /* int32 [T*k] sorted expert ids              */
+    void *permuted_rows;        /* int32 [T*k] source_rows in sorted order    */
+
+    void *first_token_offset;   /* int32 [E+1]                                */
+
+    void *expanded_seq_input;   /* fp16 [T*k, d_hidden]                       */
+    void *expanded_seq_softmax; /* fp16 [T*k]                                 */
+    void *rev_permuted_rows;    /* int32 [T*k]                                */
+
+    void *expanded_fc1_output;  /* fp16 [T*k, d_expert]                       */
+    void *expanded_fc1_gate_splitk;
+    void *expanded_fc1_up_splitk;
+    void *expanded_fc2_output;  /* fp16 [T*k, d_hidden]                       */
+    void *expanded_fc2_splitk;
+
+    void *shared_fc1_output;    /* fp16 [T, d_expert*n_shared]                */
+    void *shared_fc1_gate_splitk;
+    void *shared_fc1_up_splitk;
+    void *shared_fc2_output;    /* fp16 [T, d_hidden]                         */
+    void *shared_fc2_splitk;
+
+    void *final_output;         /* fp16 [T, d_hidden]                         */
+    void *final_output_splitk;
+} MoEInputRaw;
+
+/* Replaces `run_topk` of src/moe/moe.cpp:343 (typedef tests/moe/moe_topk_test.cpp:400).
+ * Runs the whole layer on `stream` from the router logits in
+ * input->expert_scores and fills every intermediate buffer listed above.
+ * Differences from the reference, all additive: any T, any power-of-two
+ * E <= 256, k <= 8 (reference: 7 compiled shapes, moe.cpp:421-435); honours the
+ * caller's stream; returns non-zero (RF_ERR_*) on unsupported arguments
+ * instead of printing "Failed to dispatch".  When `metrics` is non-NULL the
+ * call blocks until completion and fills the reference's 12 named entries
+ * (moe.cpp:350-364).                                                          */
+int run_topk(MoEInputRaw *input, rf_stream_t stream, PerfMetrics *metrics);
+
+/* Like run_topk but first computes expert_scores = input_seq . router_weight^T
+ * (fp16) on the device, i.e. the router GEMM the reference leaves to PyTorch
+ * (scripts/gen_submission.py:400).  `router_bias` (fp32 [E], may be NULL) is
+ * added to the logits before they are rounded to fp16.                        */
+int rf_moe_forward(MoEInputRaw *input, const float *router_bias, rf_stream_t stream, PerfMetrics *metrics);
+
+/* Replaces `initialize_workspace` of src/moe/moe.cpp:443: returns a
+ * process-lifetime device allocation big enough for the intermediates of the
+ * largest shape seen by rf_moe_workspace_reserve (default: the reference's
+ * MAX_* constants, moe.cpp:36-40).                                            */
+void initialize_workspace(void **workspace);
+
+/* Bytes of intermediates for one layer call; rf_moe_bind_workspace carves a
+ * caller buffer of that size into the intermediate fields of `input`
+ * (reference: pointer arithmetic in run_from_python, src/moe/moe.cpp:517-578). */
+size_t rf_moe_workspace_bytes(const InputParams *params);
+int rf_moe_bind_workspace(MoEInputRaw *input, void *workspace, size_t workspace_bytes);
+
+/* Replaces `run_from_python` of src/moe/moe.cpp:481-586 (python side
+ * scripts/gen_submission.py:344-350, :402).  Pointers travel as integers.
+ * expert_scores == 0 makes the library compute the router GEMM itself.
+ * Uses the library workspace; launches on `stream`.                           */
+int rf_run_from_python(int seq_len, int batch_size, int d_hidden, int d_expert, int n_routed_experts,
+                       int n_experts_per_token, int n_shared_experts, unsigned long long input_seq,
+                       unsigned long long expert_scores, const unsigned long long *expert_weight_gate_p,
+                       const unsigned long long *expert_weight_up_p,
+                       const unsigned long long *expert_weight_down_p,
+                       unsigned long long shared_expert_weight_gate, unsigned long long shared_expert_weight_up,
+                       unsigned long long shared_expert_weight_down, unsigned long long router_weight,
+                       unsigned long long final_output, rf_stream_t stream);
+
+/* Stage entry points (each is one reference kernel; used by the stage tests
+ * and by the expert-parallel driver).                                         */
+
+/* topk_kernel, src/moe/moe_topk_kernel.cpp:15-150: softmax over E fp16 logits,
+ * k rounds of arg-max with lowest-index tie break.                            */
+int rf_moe_topk(const void *expert_scores, int n_tokens, int n_experts, int top_k, void *seq_experts_index,
+                void *seq_experts_softmax, void *source_rows, rf_stream_t stream);
+
+/* sort_experts + compute_first_token_offset + the index half of expand_input
+ * (src/moe/moe.cpp:119-126, src/moe/moe_topk_kernel.cpp:152-213): stable
+ * counting sort of (expert, source_row) pairs.  `scratch` needs
+ * rf_moe_permute_scratch_bytes(n_tokens*top_k, n_experts) bytes.                             */
+size_t rf_moe_permute_scratch_bytes(int n_items, int n_experts);
+int rf_moe_permute(const void *seq_experts_index, const void *source_rows, const void *seq_experts_softmax,
+                   int n_tokens, int n_experts, int top_k, void *permuted_experts, void *permuted_rows,
+                   void *first_token_offset, void *rev_permuted_rows, void *expanded_seq_softmax, void *scratch,
+                   rf_stream_t stream);
+
+/* expand_input row gather, src/moe/moe_topk_kernel.cpp:174-213.               */
+int rf_moe_gather_rows(const void *input_seq, const void *permuted_rows, int n_tokens, int n_rows, int d_hidden,
+                       void *expanded_seq_input, rf_stream_t stream);
+
+/* Grouped expert GEMM over the row ranges group_offsets_dev[g]..[g+1] of x [n_rows, k_dim] fp16
+ * (LaunchGroupGEMM, src/moe/gemm_thirdparty.cpp:65-115; one group = LaunchGEMM, :261-288).
+ * `w_ptrs_host` is a HOST array of n_groups device pointers to fp16 [k_dim, n_dim] row-major
+ * weights, as in MoEInputRaw.  With `w2_ptrs_host` != NULL the kernel computes
+ * fp16(SiLU(fp16(X.W)) * fp16(X.W2)), the fused form of the two GEMMs plus moe_gemm_reduce_ab
+ * (src/moe/moe_gemm_pipeline_kernel.cpp:51, :377-405).  n_dim % 64 == 0, k_dim % 64 == 0.
+ * Row counts stay on the device (the reference copies them to the host, src/moe/moe.cpp:204). */
+int rf_moe_grouped_gemm(const void *x, int n_rows, const void *const *w_ptrs_host,
+                        const void *const *w2_ptrs_host, const int *group_offsets_dev, int n_groups, int n_dim,
+                        int k_dim, void *out, rf_stream_t stream);
+
+/* Router logits expert_scores[t, e] = fp16(x[t,:] . router_weight[e,:] + router_bias[e]); the
+ * matmul the reference leaves to PyTorch (scripts/gen_submission.py:400).  router_bias may be NULL. */
+int rf_moe_router_gemm(const void *x, const void *router_weight, const float *router_bias, int n_tokens,
+                       int n_experts, int d_hidden, void *expert_scores, rf_stream_t stream);
+
+/* reduce_output, src/moe/moe_topk_kernel.cpp:215-251.                         */
+int rf_moe_combine(const void *expanded_fc2_output, const void *shared_fc2_output, const void *rev_permuted_rows,
+                   const void *expanded_seq_softmax, int n_tokens, int top_k, int d_hidden, void *final_output,
+                   rf_stream_t stream);
+
 /* Library / build identification: "rf_b200 <version> sm_100a".               */
 const char *rf_version(void);
 

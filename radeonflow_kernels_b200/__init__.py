@@ -6,5 +6,6 @@ of the reference's Python-level boundary (scripts/gen_submission.py:247-262,
 """
 from . import _lib  # noqa: F401
 from .gemm import custom_kernel as gemm_custom_kernel, fp8_mm  # noqa: F401
+from .moe import custom_kernel as moe_custom_kernel, moe_forward  # noqa: F401
 
-__all__ = ["fp8_mm", "gemm_custom_kernel"]
+__all__ = ["fp8_mm", "gemm_custom_kernel", "moe_custom_kernel", "moe_forward"]

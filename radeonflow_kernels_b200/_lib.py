@@ -90,6 +90,37 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_fp8_gemm_workspace_bytes.argtypes = [ci, ci, ci, ci]
     L.rf_fp8_gemm_choose_split.restype = ci
     L.rf_fp8_gemm_choose_split.argtypes = [ci, ci, ci]
+    # ---- MoE
+    pm = ctypes.POINTER(PerfMetrics)
+    raw = ctypes.POINTER(MoEInputRaw)
+    ull = ctypes.c_ulonglong
+    pull = ctypes.POINTER(ull)
+    L.run_topk.restype = ci
+    L.run_topk.argtypes = [raw, vp, pm]
+    L.rf_moe_forward.restype = ci
+    L.rf_moe_forward.argtypes = [raw, vp, vp, pm]
+    L.initialize_workspace.restype = None
+    L.initialize_workspace.argtypes = [ctypes.POINTER(vp)]
+    L.rf_moe_workspace_bytes.restype = sz
+    L.rf_moe_workspace_bytes.argtypes = [ctypes.POINTER(InputParams)]
+    L.rf_moe_bind_workspace.restype = ci
+    L.rf_moe_bind_workspace.argtypes = [raw, vp, sz]
+    L.rf_run_from_python.restype = ci
+    L.rf_run_from_python.argtypes = [ci] * 7 + [ull, ull, pull, pull, pull, ull, ull, ull, ull, ull, vp]
+    L.rf_moe_topk.restype = ci
+    L.rf_moe_topk.argtypes = [vp, ci, ci, ci, vp, vp, vp, vp]
+    L.rf_moe_permute_scratch_bytes.restype = sz
+    L.rf_moe_permute_scratch_bytes.argtypes = [ci, ci]
+    L.rf_moe_permute.restype = ci
+    L.rf_moe_permute.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp]
+    L.rf_moe_gather_rows.restype = ci
+    L.rf_moe_gather_rows.argtypes = [vp, vp, ci, ci, ci, vp, vp]
+    L.rf_moe_grouped_gemm.restype = ci
+    L.rf_moe_grouped_gemm.argtypes = [vp, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), vp, ci, ci, ci, vp, vp]
+    L.rf_moe_router_gemm.restype = ci
+    L.rf_moe_router_gemm.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp]
+    L.rf_moe_combine.restype = ci
+    L.rf_moe_combine.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, vp]
 
 
 def check(status: int, what: str) -> None:

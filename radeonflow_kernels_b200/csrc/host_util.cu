@@ -44,24 +44,25 @@ DeviceState* device_state() {
     return st;
 }
 
-void* device_scratch(size_t bytes) {
+void* device_scratch(size_t bytes, int slot) {
     DeviceState* st = device_state();
-    if (!st) return nullptr;
-    if (bytes <= st->scratch_bytes) return st->scratch;
+    if (!st || slot < 0 || slot > 2) return nullptr;
+    if (bytes <= st->scratch_bytes[slot]) return st->scratch[slot];
     std::lock_guard<std::mutex> lock(g_mu);
-    if (bytes <= st->scratch_bytes) return st->scratch;
+    if (bytes <= st->scratch_bytes[slot]) return st->scratch[slot];
     // Work already queued may still use the old buffer.
     if (cudaDeviceSynchronize() != cudaSuccess) return nullptr;
-    if (st->scratch) cudaFree(st->scratch);
-    st->scratch = nullptr;
-    st->scratch_bytes = 0;
+    if (st->scratch[slot]) cudaFree(st->scratch[slot]);
+    st->scratch[slot] = nullptr;
+    st->scratch_bytes[slot] = 0;
     size_t want = bytes + (bytes >> 2);  // 25 % head-room so slowly growing shapes do not thrash
-    if (cudaMalloc(&st->scratch, want) != cudaSuccess) {
-        if (cudaMalloc(&st->scratch, bytes) != cudaSuccess) return nullptr;
+    if (cudaMalloc(&st->scratch[slot], want) != cudaSuccess) {
+        cudaGetLastError();
+        if (cudaMalloc(&st->scratch[slot], bytes) != cudaSuccess) return nullptr;
         want = bytes;
     }
-    st->scratch_bytes = want;
-    return st->scratch;
+    st->scratch_bytes[slot] = want;
+    return st->scratch[slot];
 }
 
 bool encode_tma_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,

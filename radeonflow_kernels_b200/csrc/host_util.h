@@ -15,17 +15,23 @@ struct DeviceState {
     bool init = false;
     int num_sms = 0;
     int* status = nullptr;          // device status word
-    void* scratch = nullptr;        // library-owned scratch (split-K slices, MoE intermediates)
-    size_t scratch_bytes = 0;
+    void* scratch[3] = {nullptr, nullptr, nullptr};   // library-owned growable buffers, see ScratchSlot
+    size_t scratch_bytes[3] = {0, 0, 0};
+};
+
+enum ScratchSlot {
+    kScratchGemm = 0,      // split-K slices of the FP8 GEMM
+    kScratchMoeAux = 1,    // MoE tile lists and sort counters
+    kScratchMoeWork = 2,   // MoE intermediates handed out by initialize_workspace
 };
 
 // State of the current device; initialises it on first use (allocates the
 // 4-byte status word).  Returns nullptr when a CUDA call fails.
 DeviceState* device_state();
 
-// Library-owned scratch of at least `bytes` on the current device (grows by
+// Library-owned buffer `slot` of at least `bytes` on the current device (grows by
 // freeing and re-allocating; synchronises the device when it grows).
-void* device_scratch(size_t bytes);
+void* device_scratch(size_t bytes, int slot = kScratchGemm);
 
 // 2-D row-major tensor map: `rows` x `cols` elements of `elem_bytes`, row
 // pitch `pitch_bytes`; box = box_rows x box_cols; 128-byte swizzle when

@@ -1,0 +1,480 @@
+// C-ABI entry points of the MoE layer (declared in include/rf_b200.h): stage sequencing, workspace
+// carving, per-expert tensor-map cache, per-stage timing.  Host code only; kernels live in
+// moe_route.cu and moe_gemm.cu.
+#include "../../include/rf_b200.h"
+#include "host_util.h"
+#include "moe_kernels.h"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+namespace {
+
+using rf::DeviceState;
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+int validate_params(const InputParams& q) {
+    const long long t = (long long)q.batch_size * q.seq_len;
+    if (t <= 0 || t > (1 << 24)) return RF_ERR_BAD_SHAPE;
+    if (q.d_hidden <= 0 || q.d_hidden % 64 != 0 || q.d_expert <= 0 || q.d_expert % 64 != 0) return RF_ERR_BAD_SHAPE;
+    if (!is_pow2(q.n_routed_experts) || q.n_routed_experts > 256) return RF_ERR_UNSUPPORTED;
+    if (q.n_experts_per_token < 1 || q.n_experts_per_token > 8 || q.n_experts_per_token > q.n_routed_experts)
+        return RF_ERR_UNSUPPORTED;
+    if (q.n_shared_experts < 1) return RF_ERR_UNSUPPORTED;
+    return RF_OK;
+}
+
+// ---------------------------------------------------------------- per-expert tensor-map cache --
+// Weights are static across calls, so the device array of tensor maps built for a set of weight
+// pointers is kept and found again by (pointers, shape).
+struct MapSet {
+    int device;
+    int rows, cols, box_rows, box_cols;
+    std::vector<const void*> ptrs;
+    CUtensorMap* dev_maps;
+};
+std::mutex g_map_mu;
+std::vector<MapSet> g_map_sets;
+
+// Row-major fp16 matrices [rows, cols]; one map per pointer; returns a device array.
+const CUtensorMap* weight_maps(const void* const* ptrs, int count, int rows, int cols, int box_rows, int box_cols) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    for (const MapSet& m : g_map_sets) {
+        if (m.device == dev && m.rows == rows && m.cols == cols && m.box_rows == box_rows && m.box_cols == box_cols &&
+            (int)m.ptrs.size() == count && memcmp(m.ptrs.data(), ptrs, sizeof(void*) * count) == 0)
+            return m.dev_maps;
+    }
+    std::vector<CUtensorMap> host(count);
+    for (int i = 0; i < count; ++i) {
+        if (!ptrs[i] || ((uintptr_t)ptrs[i] & 15)) return nullptr;
+        if (!rf::encode_tma_2d(&host[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ptrs[i], (uint64_t)rows, (uint64_t)cols,
+                               (uint64_t)cols * 2, (uint32_t)box_rows, (uint32_t)box_cols, true))
+            return nullptr;
+    }
+    MapSet m;
+    m.device = dev;
+    m.rows = rows; m.cols = cols; m.box_rows = box_rows; m.box_cols = box_cols;
+    m.ptrs.assign(ptrs, ptrs + count);
+    m.dev_maps = nullptr;
+    if (cudaMalloc(&m.dev_maps, sizeof(CUtensorMap) * count) != cudaSuccess) return nullptr;
+    if (cudaMemcpy(m.dev_maps, host.data(), sizeof(CUtensorMap) * count, cudaMemcpyHostToDevice) != cudaSuccess)
+        return nullptr;
+    if (g_map_sets.size() >= 64) {   // bounded: drop the oldest set
+        cudaDeviceSynchronize();
+        cudaFree(g_map_sets.front().dev_maps);
+        g_map_sets.erase(g_map_sets.begin());
+    }
+    g_map_sets.push_back(m);
+    return m.dev_maps;
+}
+
+// ------------------------------------------------------------------------------ aux scratch --
+struct Aux {
+    int* tile_group;
+    int* tile_row0;
+    int* tile_count;
+    int* single_offsets;   // [2] = {0, T} for the shared expert / router (one group)
+    int* sort_scratch;
+};
+
+size_t aux_bytes(int n_rows_expanded, int n_experts) {
+    const size_t max_tiles = (size_t)n_rows_expanded / 128 + n_experts + 2;
+    return align_up(max_tiles * 4, 256) * 2 + 256 + 256 +
+           align_up(rf::moe_permute_scratch_bytes(n_rows_expanded, n_experts), 256);
+}
+
+bool carve_aux(Aux* a, int n_rows_expanded, int n_experts) {
+    const size_t max_tiles = (size_t)n_rows_expanded / 128 + n_experts + 2;
+    char* base = static_cast<char*>(rf::device_scratch(aux_bytes(n_rows_expanded, n_experts), rf::kScratchMoeAux));
+    if (!base) return false;
+    a->tile_group = reinterpret_cast<int*>(base);
+    base += align_up(max_tiles * 4, 256);
+    a->tile_row0 = reinterpret_cast<int*>(base);
+    base += align_up(max_tiles * 4, 256);
+    a->tile_count = reinterpret_cast<int*>(base);
+    base += 256;
+    a->single_offsets = reinterpret_cast<int*>(base);
+    base += 256;
+    a->sort_scratch = reinterpret_cast<int*>(base);
+    return true;
+}
+
+// ------------------------------------------------------------------------------ stage timer --
+struct StageTimer {
+    PerfMetrics* pm;
+    cudaStream_t stream;
+    cudaEvent_t ev[26];
+    int used = 0;
+    struct Span { int idx, a, b; double flops; };
+    std::vector<Span> spans;
+    StageTimer(PerfMetrics* m, cudaStream_t s) : pm(m), stream(s) {}
+    int mark() {
+        if (!pm || used >= 26) return -1;
+        cudaEventCreate(&ev[used]);
+        cudaEventRecord(ev[used], stream);
+        return used++;
+    }
+    void span(int idx, int a, int b, double flops) {
+        if (pm && a >= 0 && b >= 0) spans.push_back({idx, a, b, flops});
+    }
+    void finish() {
+        if (!pm) return;
+        static const char* names[12] = {"overall", "moe_misc", "transpose", "routed_fc1", "routed_fc2", "shared_fc1",
+                                        "shared_fc2", "routed_fc1_reduce", "routed_fc2_reduce", "shared_fc1_reduce",
+                                        "shared_fc2_reduce", "reduce_output"};
+        pm->count = 12;
+        for (int i = 0; i < 12; ++i) {
+            memset(pm->entries[i].name, 0, sizeof(pm->entries[i].name));
+            strncpy(pm->entries[i].name, names[i], sizeof(pm->entries[i].name) - 1);
+            pm->entries[i].time = 0.f;
+            pm->entries[i].gflops = 0.f;
+        }
+        if (used > 0) cudaEventSynchronize(ev[used - 1]);
+        for (const Span& s : spans) {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, ev[s.a], ev[s.b]);
+            pm->entries[s.idx].time += ms;
+            if (ms > 0.f) pm->entries[s.idx].gflops = (float)(s.flops / (ms * 1e-3) / 1e9);
+        }
+        for (int i = 0; i < used; ++i) cudaEventDestroy(ev[i]);
+    }
+};
+
+// One grouped GEMM: rows of `x` [n_rows, k] by per-group weights; `offsets_dev` has n_groups+1 entries.
+int grouped_gemm(int mode, const void* x, int n_rows, const void* const* w_host, const void* const* w2_host,
+                 int n_groups, const int* offsets_dev, int n_out, int k, const float* bias, void* out, const Aux& aux,
+                 DeviceState* st, cudaStream_t stream) {
+    if (n_rows <= 0) return RF_OK;
+    const CUtensorMap* maps;
+    const CUtensorMap* maps2 = nullptr;
+    if (mode == rf::kMoeGemmRouter) {
+        maps = weight_maps(w_host, 1, n_out, k, 256, 64);            // [N, K] row-major, box 256 rows x 64 K
+    } else {
+        maps = weight_maps(w_host, n_groups, k, n_out, 64, 64);      // [K, N] row-major, box 64 K-rows x 64 N
+        if (mode == rf::kMoeGemmSwiglu) maps2 = weight_maps(w2_host, n_groups, k, n_out, 64, 64);
+    }
+    if (!maps || (mode == rf::kMoeGemmSwiglu && !maps2)) return RF_ERR_CUDA;
+    CUtensorMap ta, to;
+    if (!rf::encode_tma_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)n_rows, (uint64_t)k, (uint64_t)k * 2,
+                           128, 64, true))
+        return RF_ERR_CUDA;
+    const bool tma_store = (n_out % 64) == 0;
+    if (tma_store) {
+        if (!rf::encode_tma_2d(&to, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, (uint64_t)n_rows, (uint64_t)n_out,
+                               (uint64_t)n_out * 2, 32, 64, true))
+            return RF_ERR_CUDA;
+    } else {
+        to = ta;
+    }
+    if (rf::moe_tile_list_launch(offsets_dev, n_groups, aux.tile_group, aux.tile_row0, aux.tile_count, stream) !=
+        cudaSuccess)
+        return RF_ERR_CUDA;
+    rf::MoeGemmParams p;
+    p.tile_group = aux.tile_group;
+    p.tile_row0 = aux.tile_row0;
+    p.tile_count = aux.tile_count;
+    p.group_offsets = offsets_dev;
+    p.b_maps = maps;
+    p.b2_maps = maps2;
+    p.bias = bias;
+    p.out = out;
+    p.n_out = n_out;
+    p.k = k;
+    p.tma_store = tma_store ? 1 : 0;
+    p.status = st->status;
+    if (rf::moe_gemm_launch(mode, ta, to, p, st->num_sms, stream) != cudaSuccess) return RF_ERR_CUDA;
+    return RF_OK;
+}
+
+int set_single_offsets(const Aux& aux, int n_rows, cudaStream_t stream) {
+    return rf::moe_set_range_launch(aux.single_offsets, 0, n_rows, stream) == cudaSuccess ? RF_OK : RF_ERR_CUDA;
+}
+
+int moe_layer(MoEInputRaw* in, bool compute_router, const float* router_bias, cudaStream_t stream,
+              PerfMetrics* metrics) {
+    if (!in) return RF_ERR_NULL_POINTER;
+    const InputParams& q = in->params;
+    int rc = validate_params(q);
+    if (rc != RF_OK) return rc;
+    const int T = q.batch_size * q.seq_len;
+    const int d = q.d_hidden, f = q.d_expert, E = q.n_routed_experts, K = q.n_experts_per_token;
+    const int fs = f * q.n_shared_experts;
+    const int TK = T * K;
+    const void* need[] = {in->expert_weight_gate, in->expert_weight_up, in->expert_weight_down, in->input_seq,
+                          in->shared_expert_weight_gate, in->shared_expert_weight_up, in->shared_expert_weight_down,
+                          in->expert_scores, in->seq_experts_index, in->seq_experts_softmax, in->source_rows,
+                          in->permuted_experts, in->permuted_rows, in->first_token_offset, in->expanded_seq_input,
+                          in->expanded_seq_softmax, in->rev_permuted_rows, in->expanded_fc1_output,
+                          in->expanded_fc2_output, in->shared_fc1_output, in->shared_fc2_output, in->final_output};
+    for (const void* ptr : need)
+        if (!ptr) return RF_ERR_NULL_POINTER;
+    if (compute_router && !in->router_weight) return RF_ERR_NULL_POINTER;
+    DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    Aux aux;
+    if (!carve_aux(&aux, TK > T ? TK : T, E)) return RF_ERR_CUDA;
+
+    StageTimer tm(metrics, stream);
+    const int t_begin = tm.mark();
+    if ((rc = set_single_offsets(aux, T, stream)) != RF_OK) return rc;
+
+    // ---- router GEMM (optional), softmax + top-k, counting sort, row gather  -> "moe_misc"
+    if (compute_router) {
+        const void* rw[1] = {in->router_weight};
+        rc = grouped_gemm(rf::kMoeGemmRouter, in->input_seq, T, rw, nullptr, 1, aux.single_offsets, E, d, router_bias,
+                          in->expert_scores, aux, st, stream);
+        if (rc != RF_OK) return rc;
+    }
+    if (rf::moe_topk_launch(in->expert_scores, T, E, K, in->seq_experts_index, in->seq_experts_softmax,
+                            in->source_rows, stream) != cudaSuccess)
+        return RF_ERR_CUDA;
+    if (rf::moe_permute_launch(in->seq_experts_index, in->source_rows, in->seq_experts_softmax, TK, E,
+                               in->permuted_experts, in->permuted_rows, in->first_token_offset, in->rev_permuted_rows,
+                               in->expanded_seq_softmax, aux.sort_scratch, stream) != cudaSuccess)
+        return RF_ERR_CUDA;
+    if (rf::moe_gather_rows_launch(in->input_seq, static_cast<const int*>(in->permuted_rows), T, TK, d * 2,
+                                   in->expanded_seq_input, st->num_sms, stream) != cudaSuccess)
+        return RF_ERR_CUDA;
+    const int t_misc = tm.mark();
+    tm.span(1, t_begin, t_misc, 0.0);
+
+    // ---- routed experts: fc1 (gate and up in one pass, SwiGLU in the epilogue), fc2
+    rc = grouped_gemm(rf::kMoeGemmSwiglu, in->expanded_seq_input, TK, in->expert_weight_gate, in->expert_weight_up, E,
+                      static_cast<const int*>(in->first_token_offset), f, d, nullptr, in->expanded_fc1_output, aux, st,
+                      stream);
+    if (rc != RF_OK) return rc;
+    const int t_fc1 = tm.mark();
+    tm.span(3, t_misc, t_fc1, 2.0 * TK * (double)f * d * 2);
+    rc = grouped_gemm(rf::kMoeGemmPlain, in->expanded_fc1_output, TK, in->expert_weight_down, nullptr, E,
+                      static_cast<const int*>(in->first_token_offset), d, f, nullptr, in->expanded_fc2_output, aux, st,
+                      stream);
+    if (rc != RF_OK) return rc;
+    const int t_fc2 = tm.mark();
+    tm.span(4, t_fc1, t_fc2, 2.0 * TK * (double)f * d);
+
+    // ---- shared expert over all tokens
+    const void* sg[1] = {in->shared_expert_weight_gate};
+    const void* su[1] = {in->shared_expert_weight_up};
+    const void* sd[1] = {in->shared_expert_weight_down};
+    rc = grouped_gemm(rf::kMoeGemmSwiglu, in->input_seq, T, sg, su, 1, aux.single_offsets, fs, d, nullptr,
+                      in->shared_fc1_output, aux, st, stream);
+    if (rc != RF_OK) return rc;
+    const int t_s1 = tm.mark();
+    tm.span(5, t_fc2, t_s1, 2.0 * T * (double)fs * d * 2);
+    rc = grouped_gemm(rf::kMoeGemmPlain, in->shared_fc1_output, T, sd, nullptr, 1, aux.single_offsets, d, fs, nullptr,
+                      in->shared_fc2_output, aux, st, stream);
+    if (rc != RF_OK) return rc;
+    const int t_s2 = tm.mark();
+    tm.span(6, t_s1, t_s2, 2.0 * T * (double)fs * d);
+
+    // ---- weighted combine + shared add
+    if (rf::moe_combine_launch(in->expanded_fc2_output, in->shared_fc2_output,
+                               static_cast<const int*>(in->rev_permuted_rows), in->expanded_seq_softmax, T, K, d * 2,
+                               in->final_output, stream) != cudaSuccess)
+        return RF_ERR_CUDA;
+    const int t_end = tm.mark();
+    tm.span(11, t_s2, t_end, 0.0);
+    tm.span(0, t_begin, t_end, 2.0 * (double)d * f * 3.0 * ((double)TK + (double)T * q.n_shared_experts));
+    tm.finish();
+    return RF_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int run_topk(MoEInputRaw* input, rf_stream_t stream, PerfMetrics* metrics) {
+    return moe_layer(input, false, nullptr, reinterpret_cast<cudaStream_t>(stream), metrics);
+}
+
+int rf_moe_forward(MoEInputRaw* input, const float* router_bias, rf_stream_t stream, PerfMetrics* metrics) {
+    return moe_layer(input, true, router_bias, reinterpret_cast<cudaStream_t>(stream), metrics);
+}
+
+size_t rf_moe_workspace_bytes(const InputParams* q) {
+    if (!q || validate_params(*q) != RF_OK) return 0;
+    const size_t T = (size_t)q->batch_size * q->seq_len, K = q->n_experts_per_token, E = q->n_routed_experts;
+    const size_t d = q->d_hidden, f = q->d_expert, fs = f * q->n_shared_experts, TK = T * K;
+    size_t b = 0;
+    auto add = [&](size_t n) { b += align_up(n, 256); };
+    add(T * E * 2);            // expert_scores
+    add(TK * 4); add(TK * 2); add(TK * 4);           // seq_experts_index, seq_experts_softmax, source_rows
+    add(TK * 4); add(TK * 4); add((E + 1) * 4);      // permuted_experts, permuted_rows, first_token_offset
+    add(TK * d * 2); add(TK * 2); add(TK * 4);       // expanded_seq_input, expanded_seq_softmax, rev_permuted_rows
+    add(TK * f * 2); add(TK * d * 2);                // expanded_fc1_output, expanded_fc2_output
+    add(T * fs * 2); add(T * d * 2);                 // shared_fc1_output, shared_fc2_output
+    return b;
+}
+
+int rf_moe_bind_workspace(MoEInputRaw* in, void* workspace, size_t workspace_bytes) {
+    if (!in || !workspace) return RF_ERR_NULL_POINTER;
+    const size_t need = rf_moe_workspace_bytes(&in->params);
+    if (need == 0) return RF_ERR_BAD_SHAPE;
+    if (workspace_bytes < need) return RF_ERR_WORKSPACE;
+    if ((uintptr_t)workspace & 255) return RF_ERR_MISALIGNED;
+    const InputParams* q = &in->params;
+    const size_t T = (size_t)q->batch_size * q->seq_len, K = q->n_experts_per_token, E = q->n_routed_experts;
+    const size_t d = q->d_hidden, f = q->d_expert, fs = f * q->n_shared_experts, TK = T * K;
+    char* pcur = static_cast<char*>(workspace);
+    auto take = [&](size_t n) { void* r = pcur; pcur += align_up(n, 256); return r; };
+    if (!in->expert_scores) in->expert_scores = take(T * E * 2); else take(T * E * 2);
+    in->seq_experts_index = take(TK * 4);
+    in->seq_experts_softmax = take(TK * 2);
+    in->source_rows = take(TK * 4);
+    in->permuted_experts = take(TK * 4);
+    in->permuted_rows = take(TK * 4);
+    in->first_token_offset = take((E + 1) * 4);
+    in->expanded_seq_input = take(TK * d * 2);
+    in->expanded_seq_softmax = take(TK * 2);
+    in->rev_permuted_rows = take(TK * 4);
+    in->expanded_fc1_output = take(TK * f * 2);
+    in->expanded_fc2_output = take(TK * d * 2);
+    in->shared_fc1_output = take(T * fs * 2);
+    in->shared_fc2_output = take(T * d * 2);
+    return RF_OK;
+}
+
+void initialize_workspace(void** workspace) {
+    // src/moe/moe.cpp:36-40: MAX_SEQ_LEN 8192, MAX_N_EXPERT_PER_TOKEN 4, 7168 / 2048, 32 experts
+    InputParams q = {1, 8192, 7168, 2048, 32, 4, 1, 0};
+    void* p = rf::device_scratch(rf_moe_workspace_bytes(&q), rf::kScratchMoeWork);
+    if (workspace) *workspace = p;
+}
+
+int rf_run_from_python(int seq_len, int batch_size, int d_hidden, int d_expert, int n_routed_experts,
+                       int n_experts_per_token, int n_shared_experts, unsigned long long input_seq,
+                       unsigned long long expert_scores, const unsigned long long* expert_weight_gate_p,
+                       const unsigned long long* expert_weight_up_p, const unsigned long long* expert_weight_down_p,
+                       unsigned long long shared_expert_weight_gate, unsigned long long shared_expert_weight_up,
+                       unsigned long long shared_expert_weight_down, unsigned long long router_weight,
+                       unsigned long long final_output, rf_stream_t stream) {
+    if (!expert_weight_gate_p || !expert_weight_up_p || !expert_weight_down_p) return RF_ERR_NULL_POINTER;
+    MoEInputRaw in;
+    memset(&in, 0, sizeof(in));
+    in.params = InputParams{batch_size, seq_len, d_hidden, d_expert, n_routed_experts, n_experts_per_token,
+                            n_shared_experts, 0};
+    int rc = validate_params(in.params);
+    if (rc != RF_OK) return rc;
+    std::vector<void*> g(n_routed_experts), u(n_routed_experts), dn(n_routed_experts);
+    for (int i = 0; i < n_routed_experts; ++i) {
+        g[i] = reinterpret_cast<void*>(expert_weight_gate_p[i]);
+        u[i] = reinterpret_cast<void*>(expert_weight_up_p[i]);
+        dn[i] = reinterpret_cast<void*>(expert_weight_down_p[i]);
+    }
+    in.expert_weight_gate = g.data();
+    in.expert_weight_up = u.data();
+    in.expert_weight_down = dn.data();
+    in.input_seq = reinterpret_cast<void*>(input_seq);
+    in.shared_expert_weight_gate = reinterpret_cast<void*>(shared_expert_weight_gate);
+    in.shared_expert_weight_up = reinterpret_cast<void*>(shared_expert_weight_up);
+    in.shared_expert_weight_down = reinterpret_cast<void*>(shared_expert_weight_down);
+    in.router_weight = reinterpret_cast<void*>(router_weight);
+    in.expert_scores = reinterpret_cast<void*>(expert_scores);
+    in.final_output = reinterpret_cast<void*>(final_output);
+    const size_t need = rf_moe_workspace_bytes(&in.params);
+    void* ws = rf::device_scratch(need, rf::kScratchMoeWork);
+    if (!ws) return RF_ERR_CUDA;
+    rc = rf_moe_bind_workspace(&in, ws, need);
+    if (rc != RF_OK) return rc;
+    return moe_layer(&in, expert_scores == 0, nullptr, reinterpret_cast<cudaStream_t>(stream), nullptr);
+}
+
+int rf_moe_topk(const void* expert_scores, int n_tokens, int n_experts, int top_k, void* seq_experts_index,
+                void* seq_experts_softmax, void* source_rows, rf_stream_t stream) {
+    if (!expert_scores || !seq_experts_index || !seq_experts_softmax || !source_rows) return RF_ERR_NULL_POINTER;
+    if (n_tokens < 0 || !is_pow2(n_experts) || n_experts > 256 || top_k < 1 || top_k > 8 || top_k > n_experts)
+        return RF_ERR_UNSUPPORTED;
+    if (n_tokens == 0) return RF_OK;
+    return rf::moe_topk_launch(expert_scores, n_tokens, n_experts, top_k, seq_experts_index, seq_experts_softmax,
+                               source_rows, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? RF_OK : RF_ERR_CUDA;
+}
+
+size_t rf_moe_permute_scratch_bytes(int n_items, int n_experts) {
+    return rf::moe_permute_scratch_bytes(n_items, n_experts);
+}
+
+int rf_moe_permute(const void* seq_experts_index, const void* source_rows, const void* seq_experts_softmax,
+                   int n_tokens, int n_experts, int top_k, void* permuted_experts, void* permuted_rows,
+                   void* first_token_offset, void* rev_permuted_rows, void* expanded_seq_softmax, void* scratch,
+                   rf_stream_t stream) {
+    if (!seq_experts_index || !source_rows || !seq_experts_softmax || !permuted_experts || !permuted_rows ||
+        !first_token_offset || !rev_permuted_rows || !expanded_seq_softmax || !scratch)
+        return RF_ERR_NULL_POINTER;
+    if (n_tokens < 0 || n_experts < 1 || n_experts > 1024 || top_k < 1) return RF_ERR_UNSUPPORTED;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (n_tokens == 0)
+        return cudaMemsetAsync(first_token_offset, 0, (n_experts + 1) * sizeof(int), s) == cudaSuccess ? RF_OK
+                                                                                                        : RF_ERR_CUDA;
+    return rf::moe_permute_launch(seq_experts_index, source_rows, seq_experts_softmax, n_tokens * top_k, n_experts,
+                                  permuted_experts, permuted_rows, first_token_offset, rev_permuted_rows,
+                                  expanded_seq_softmax, scratch, s) == cudaSuccess
+               ? RF_OK : RF_ERR_CUDA;
+}
+
+int rf_moe_gather_rows(const void* input_seq, const void* permuted_rows, int n_tokens, int n_rows, int d_hidden,
+                       void* expanded_seq_input, rf_stream_t stream) {
+    if (!input_seq || !permuted_rows || !expanded_seq_input) return RF_ERR_NULL_POINTER;
+    if (d_hidden <= 0 || d_hidden % 8 != 0 || n_tokens <= 0 || n_rows < 0) return RF_ERR_BAD_SHAPE;
+    DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    return rf::moe_gather_rows_launch(input_seq, static_cast<const int*>(permuted_rows), n_tokens, n_rows,
+                                      d_hidden * 2, expanded_seq_input, st->num_sms,
+                                      reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? RF_OK : RF_ERR_CUDA;
+}
+
+int rf_moe_grouped_gemm(const void* x, int n_rows, const void* const* w_ptrs_host, const void* const* w2_ptrs_host,
+                        const int* group_offsets_dev, int n_groups, int n_dim, int k_dim, void* out,
+                        rf_stream_t stream) {
+    if (!x || !w_ptrs_host || !group_offsets_dev || !out) return RF_ERR_NULL_POINTER;
+    if (n_rows < 0 || n_groups < 1 || n_groups > 1024 || n_dim <= 0 || n_dim % 64 != 0 || k_dim <= 0 ||
+        k_dim % 64 != 0)
+        return RF_ERR_BAD_SHAPE;
+    DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    Aux aux;
+    if (!carve_aux(&aux, n_rows, n_groups)) return RF_ERR_CUDA;
+    return grouped_gemm(w2_ptrs_host ? rf::kMoeGemmSwiglu : rf::kMoeGemmPlain, x, n_rows, w_ptrs_host, w2_ptrs_host,
+                        n_groups, group_offsets_dev, n_dim, k_dim, nullptr, out, aux, st,
+                        reinterpret_cast<cudaStream_t>(stream));
+}
+
+int rf_moe_router_gemm(const void* x, const void* router_weight, const float* router_bias, int n_tokens,
+                       int n_experts, int d_hidden, void* expert_scores, rf_stream_t stream) {
+    if (!x || !router_weight || !expert_scores) return RF_ERR_NULL_POINTER;
+    if (n_tokens < 0 || n_experts < 1 || n_experts > 256 || d_hidden <= 0 || d_hidden % 64 != 0)
+        return RF_ERR_BAD_SHAPE;
+    DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    Aux aux;
+    if (!carve_aux(&aux, n_tokens, 1)) return RF_ERR_CUDA;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    int rc = set_single_offsets(aux, n_tokens, s);
+    if (rc != RF_OK) return rc;
+    const void* rw[1] = {router_weight};
+    return grouped_gemm(rf::kMoeGemmRouter, x, n_tokens, rw, nullptr, 1, aux.single_offsets, n_experts, d_hidden,
+                        router_bias, expert_scores, aux, st, s);
+}
+
+int rf_moe_combine(const void* expanded_fc2_output, const void* shared_fc2_output, const void* rev_permuted_rows,
+                   const void* expanded_seq_softmax, int n_tokens, int top_k, int d_hidden, void* final_output,
+                   rf_stream_t stream) {
+    if (!expanded_fc2_output || !shared_fc2_output || !rev_permuted_rows || !expanded_seq_softmax || !final_output)
+        return RF_ERR_NULL_POINTER;
+    if (n_tokens < 0 || top_k < 1 || top_k > 8 || d_hidden <= 0 || d_hidden % 8 != 0) return RF_ERR_BAD_SHAPE;
+    return rf::moe_combine_launch(expanded_fc2_output, shared_fc2_output, static_cast<const int*>(rev_permuted_rows),
+                                  expanded_seq_softmax, n_tokens, top_k, d_hidden * 2, final_output,
+                                  reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? RF_OK : RF_ERR_CUDA;
+}
+
+}  // extern "C"

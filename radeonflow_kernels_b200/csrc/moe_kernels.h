@@ -1,0 +1,52 @@
+// Internal interface between the C-ABI layer and the MoE kernels.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace rf {
+
+// ---- routing / data movement (moe_route.cu)
+cudaError_t moe_topk_launch(const void* scores, int n_tokens, int n_experts, int top_k, void* index, void* weight,
+                            void* source_rows, cudaStream_t stream);
+size_t moe_permute_scratch_bytes(int n_items, int n_experts);
+cudaError_t moe_permute_launch(const void* experts, const void* source_rows, const void* weights, int n_items,
+                               int n_experts, void* permuted_experts, void* permuted_rows, void* first_token_offset,
+                               void* rev_permuted_rows, void* expanded_softmax, void* scratch, cudaStream_t stream);
+cudaError_t moe_gather_rows_launch(const void* src, const int* row_map, int row_mod, int n_rows, int row_bytes,
+                                   void* dst, int num_sms, cudaStream_t stream);
+cudaError_t moe_combine_launch(const void* y, const void* shared_out, const int* rev, const void* expanded_softmax,
+                               int n_tokens, int top_k, int row_bytes, void* out, cudaStream_t stream);
+// dst[0] = a, dst[1] = b (a one-group offsets array written in stream order)
+cudaError_t moe_set_range_launch(int* dst, int a, int b, cudaStream_t stream);
+cudaError_t moe_tile_list_launch(const int* offsets, int n_groups, int* tile_group, int* tile_row0, int* tile_count,
+                                 cudaStream_t stream);
+
+// ---- grouped fp16 GEMM (moe_gemm.cu)
+enum MoeGemmMode {
+    kMoeGemmPlain = 0,    // out[r, n] = fp16(X[r,:] . W_g[:, n]); W_g is [K, N] row-major (N contiguous)
+    kMoeGemmSwiglu = 1,   // out[r, n] = fp16(SiLU(fp16(X.Wa_g)) * fp16(X.Wb_g))
+    kMoeGemmRouter = 2,   // out[r, n] = fp16(X[r,:] . W[n,:] + bias[n]); W is [N, K] row-major (K contiguous)
+};
+
+struct MoeGemmParams {
+    const int* tile_group;      // [n_tiles] group (expert) of each 128-row tile
+    const int* tile_row0;       // [n_tiles] first row of the tile
+    const int* tile_count;      // [1]
+    const int* group_offsets;   // [n_groups + 1] row range of each group
+    const CUtensorMap* b_maps;  // device array, one tensor map per group (first weight)
+    const CUtensorMap* b2_maps; // second weight per group (SwiGLU mode), else unused
+    const float* bias;          // router mode: optional fp32 [n_out]
+    void* out;                  // fp16 [rows, n_out]
+    int n_out;                  // output columns
+    int k;                      // reduction length (multiple of 64)
+    int tma_store;              // 1: full 32-row slabs leave through the output tensor map
+    int* status;
+};
+
+cudaError_t moe_gemm_launch(int mode, const CUtensorMap& tma_a, const CUtensorMap& tma_out, const MoeGemmParams& p,
+                            int num_sms, cudaStream_t stream);
+// Output columns covered by one tile in the given mode (256, or 128 for SwiGLU).
+int moe_gemm_tile_n(int mode);
+
+}  // namespace rf
