@@ -1,0 +1,247 @@
+"""GPU parity tests of the MoE layer: CUDA path (through the C ABI) vs the numpy oracle, stage by stage.
+
+Tolerances: rtol 1e-2 / atol 1e-2 on fp16 GEMM-derived tensors (scripts/problems/moe/reference.py:243,
+tests/moe/moe_topk_test.cpp:636-639); expert indices, permutation arrays, offsets and gate weights
+must match the oracle's rule exactly (bit for bit), given the same fp16 logits.
+"""
+import ctypes
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe as o
+from radeonflow_kernels_b200 import _lib, gemm as G, moe as M
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+RTOL = ATOL = 1e-2
+EXACT_INT = ["seq_experts_index", "source_rows", "permuted_experts", "permuted_rows", "first_token_offset",
+             "rev_permuted_rows"]
+EXACT_F16 = ["seq_experts_softmax", "expanded_seq_softmax", "expanded_seq_input"]
+CLOSE = ["expanded_fc1_output", "expanded_fc2_output", "shared_fc1_output", "shared_fc2_output", "final_output"]
+
+
+def to_dev(w):
+    return {k: torch.from_numpy(v).to(DEV) for k, v in w.items()}
+
+
+def compare_stages(got, ref):
+    for k in EXACT_INT:
+        assert np.array_equal(got[k].reshape(-1), ref[k].reshape(-1)), k
+    for k in EXACT_F16:
+        assert np.array_equal(got[k].reshape(-1).view(np.uint16), ref[k].reshape(-1).view(np.uint16)), k
+    for k in CLOSE:
+        ok, nbad, mx = o.check(got[k], ref[k], RTOL, ATOL)
+        assert ok, f"{k}: {nbad} elements out of tolerance, max abs err {mx}"
+
+
+def run_layer(x, w, cfg, logits=None, bias=None):
+    tx = torch.from_numpy(x).to(DEV)
+    tw = to_dev(w)
+    tl = torch.from_numpy(logits).to(DEV) if logits is not None else None
+    tb = torch.from_numpy(bias).to(DEV) if bias is not None else None
+    out, buf = M.moe_forward(tx, tw, cfg, expert_scores=tl, router_bias=tb)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0, "a bounded device-side wait expired"
+    return out.cpu().numpy(), {k: v.cpu().numpy() for k, v in buf.stages.items()}
+
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "moe_*.npz")))
+
+
+def load_golden(path):
+    z = np.load(path)
+    d, f, e, ns, k, t, seed = [int(v) for v in z["cfg"]]
+    w = {n[2:]: z[n] for n in z.files if n.startswith("w:")}
+    cfg = {"d_hidden": d, "d_expert": f, "n_routed_experts": e, "n_shared_experts": ns, "n_experts_per_token": k,
+           "batch_size": 1, "seq_len": t}
+    return z, w, cfg
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_against_reference_fixtures(path):
+    """End to end (router GEMM included) against the stored output of the reference's ref_kernel."""
+    z, w, cfg = load_golden(path)
+    out, got = run_layer(z["x"], w, cfg)
+    ok, nbad, mx = o.check(out, z["ref_out"], RTOL, ATOL)
+    assert ok, (nbad, mx)
+    ref = o.moe_stages(z["x"][0], w, cfg["n_routed_experts"], cfg["n_experts_per_token"], logits16=got["expert_scores"])
+    compare_stages(got, ref)
+
+
+@pytest.mark.parametrize("d,f,e,k,t,seed,zipf", [
+    (512, 256, 8, 2, 300, 5, False),
+    (1024, 512, 64, 8, 777, 6, True),
+    (256, 128, 256, 8, 1500, 7, True),
+    (192, 64, 4, 4, 130, 8, False),
+    (7168, 2048, 8, 4, 512, 9371, False),      # scripts/problems/moe/task.yml:51 shape, bs=1
+])
+def test_stage_parity(d, f, e, k, t, seed, zipf):
+    x, w, cfg = o.generate_input(d, f, e, 1, k, t, seed)
+    bias = o.zipf_router_bias(e, 1.1, seed) if zipf else None
+    _, got = run_layer(x, w, cfg, bias=bias)
+    ok, nbad, mx = o.check(got["expert_scores"], o.router_logits(x[0], w["router.weight"], bias), RTOL, ATOL)
+    assert ok, ("router logits", nbad, mx)
+    # everything downstream is compared on the logits the GPU produced (the reference's own
+    # boundary: expert_scores is an input of run_topk, src/moe/moe.h:35)
+    compare_stages(got, o.moe_stages(x[0], w, e, k, logits16=got["expert_scores"]))
+
+
+def test_run_topk_entry_with_given_logits_and_ties():
+    """`run_topk` takes the logits as input; exact fp16 ties must resolve to the lowest index."""
+    d, f, e, k, t = 256, 128, 32, 4, 257
+    x, w, cfg = o.generate_input(d, f, e, 1, k, t, 11)
+    rng = np.random.default_rng(3)
+    logits = rng.integers(-2, 3, (t, e)).astype(np.float16)       # few distinct values: ties everywhere
+    logits[5] = 0
+    out, got = run_layer(x, w, cfg, logits=logits)
+    ref = o.moe_stages(x[0], w, e, k, logits16=logits)
+    assert got["seq_experts_index"][5].tolist() == [0, 1, 2, 3]
+    compare_stages(got, ref)
+    ok, nbad, mx = o.check(out[0], ref["final_output"], RTOL, ATOL)
+    assert ok, (nbad, mx)
+
+
+@pytest.mark.parametrize("e,k", [(4, 4), (8, 2), (16, 8), (32, 4), (64, 6), (128, 8), (256, 8)])
+def test_topk_stage_bit_exact(rf_lib, e, k):
+    t = 4099
+    rng = np.random.default_rng(e * 10 + k)
+    logits = (rng.standard_normal((t, e)) * rng.standard_normal((t, 1)) * 2).astype(np.float16)
+    logits[:64] = np.round(logits[:64])              # coarse values: probability ties
+    dl = torch.from_numpy(logits).to(DEV)
+    idx = torch.empty((t, k), dtype=torch.int32, device=DEV)
+    wt = torch.empty((t, k), dtype=torch.float16, device=DEV)
+    src = torch.empty((t * k,), dtype=torch.int32, device=DEV)
+    st = rf_lib.rf_moe_topk(dl.data_ptr(), t, e, k, idx.data_ptr(), wt.data_ptr(), src.data_ptr(), None)
+    assert st == 0
+    torch.cuda.synchronize()
+    ridx, rw, rsrc = o.route(logits, k)
+    assert np.array_equal(idx.cpu().numpy(), ridx)
+    assert np.array_equal(wt.cpu().numpy().view(np.uint16), rw.view(np.uint16))
+    assert np.array_equal(src.cpu().numpy(), rsrc)
+
+
+def test_permute_stage_large_and_skewed(rf_lib):
+    """262144 pairs over 256 experts with a heavy skew and empty experts (config-4 sized)."""
+    t, k, e = 32768, 8, 256
+    rng = np.random.default_rng(0)
+    p = 1.0 / (1 + np.arange(e)) ** 1.1
+    p[200:] = 0
+    p /= p.sum()
+    idx = rng.choice(e, size=(t, k), p=p).astype(np.int32)
+    w = rng.random((t, k)).astype(np.float16)
+    src = (np.arange(k, dtype=np.int32)[None, :] * t + np.arange(t, dtype=np.int32)[:, None]).reshape(-1)
+    n = t * k
+    d_idx, d_src, d_w = (torch.from_numpy(a).to(DEV) for a in (idx, src, w))
+    outs = [torch.empty(n, dtype=torch.int32, device=DEV) for _ in range(2)]
+    first = torch.empty(e + 1, dtype=torch.int32, device=DEV)
+    rev = torch.empty(n, dtype=torch.int32, device=DEV)
+    ew = torch.empty(n, dtype=torch.float16, device=DEV)
+    scratch = torch.empty(rf_lib.rf_moe_permute_scratch_bytes(n, e), dtype=torch.uint8, device=DEV)
+    st = rf_lib.rf_moe_permute(d_idx.data_ptr(), d_src.data_ptr(), d_w.data_ptr(), t, e, k, outs[0].data_ptr(),
+                               outs[1].data_ptr(), first.data_ptr(), rev.data_ptr(), ew.data_ptr(),
+                               scratch.data_ptr(), None)
+    assert st == 0
+    torch.cuda.synchronize()
+    pe, pr, rf, rr = o.permute(idx, src, e)
+    assert np.array_equal(outs[0].cpu().numpy(), pe)
+    assert np.array_equal(outs[1].cpu().numpy(), pr)
+    assert np.array_equal(first.cpu().numpy(), rf)
+    assert np.array_equal(rev.cpu().numpy(), rr)
+    assert np.array_equal(ew.cpu().numpy().view(np.uint16), w.reshape(-1)[(pr % t) * k + pr // t].view(np.uint16))
+
+
+def test_custom_kernel_matches_moe_forward():
+    x, w, cfg = o.generate_input(512, 256, 8, 1, 2, 200, 21)
+    tx = torch.from_numpy(x).to(DEV)
+    tw = to_dev(w)
+    a = M.custom_kernel((tx, tw, cfg))
+    b, _ = M.moe_forward(tx, tw, cfg)
+    torch.cuda.synchronize()
+    assert a.shape == tx.shape
+    assert torch.equal(a, b)
+
+
+def test_perf_metrics_have_the_reference_entries():
+    x, w, cfg = o.generate_input(512, 256, 8, 1, 2, 256, 22)
+    pm = _lib.PerfMetrics()
+    M.moe_forward(torch.from_numpy(x).to(DEV), to_dev(w), cfg, metrics=pm)
+    names = [pm.entries[i].name.decode() for i in range(pm.count)]
+    assert pm.count == 12 and names[0] == "overall" and names[3] == "routed_fc1" and names[11] == "reduce_output"
+    assert pm.entries[0].time > 0 and pm.entries[3].gflops > 0
+
+
+def test_unsupported_arguments_return_status(rf_lib):
+    x, w, cfg = o.generate_input(128, 64, 8, 1, 2, 32, 1)
+    buf = M.MoEBuffers(torch.from_numpy(x).to(DEV), to_dev(w), cfg)
+    buf.raw.params.n_routed_experts = 24                    # not a power of two
+    assert rf_lib.run_topk(ctypes.byref(buf.raw), None, None) == 7
+    buf.raw.params.n_routed_experts = 8
+    buf.raw.final_output = None
+    assert rf_lib.run_topk(ctypes.byref(buf.raw), None, None) == 2
+
+
+def test_full_size_layer_spot_checked():
+    """Benchmark-sized layer (T=8192, d=7168, f=2048, E=32, k=4): integer stages exact, GEMM stages
+    spot-checked on sampled rows against the oracle (the full CPU oracle would take a minute)."""
+    d, f, e, k, t = 7168, 2048, 32, 4, 8192
+    g = torch.Generator(device=DEV)
+    g.manual_seed(1212)
+    x = torch.randn((1, t, d), device=DEV, dtype=torch.float16, generator=g)
+    w = {"router.weight": (torch.randn((e, d), device=DEV, generator=g) / d ** 0.5).half()}
+    for i in range(e):
+        w[f"experts.{i}.0.weight"] = (torch.randn((d, f), device=DEV, generator=g) / f ** 0.5).half()
+        w[f"experts.{i}.1.weight"] = (torch.randn((d, f), device=DEV, generator=g) / f ** 0.5).half()
+        w[f"experts.{i}.2.weight"] = (torch.randn((f, d), device=DEV, generator=g) / d ** 0.5).half()
+    for j, shape, s in ((0, (d, f), f), (1, (d, f), f), (2, (f, d), d)):
+        w[f"shared_experts.{j}.weight"] = (torch.randn(shape, device=DEV, generator=g) / s ** 0.5).half()
+    cfg = {"d_hidden": d, "d_expert": f, "n_routed_experts": e, "n_shared_experts": 1, "n_experts_per_token": k,
+           "batch_size": 1, "seq_len": t}
+    out, buf = M.moe_forward(x, w, cfg)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    got = {n: v.cpu().numpy() for n, v in buf.stages.items() if v.numel() < 10_000_000}
+    xh = x[0].cpu().numpy()
+    ok, nbad, mx = o.check(got["expert_scores"], o.router_logits(xh, w["router.weight"].cpu().numpy()), RTOL, ATOL)
+    assert ok, (nbad, mx)
+    ridx, rw, rsrc = o.route(got["expert_scores"], k)
+    pe, pr, first, rev = o.permute(ridx, rsrc, e)
+    for name, ref in (("seq_experts_index", ridx), ("permuted_experts", pe), ("permuted_rows", pr),
+                      ("first_token_offset", first), ("rev_permuted_rows", rev)):
+        assert np.array_equal(got[name].reshape(-1), ref.reshape(-1)), name
+    assert np.array_equal(got["seq_experts_softmax"].view(np.uint16), rw.view(np.uint16))
+    # sampled rows of the expert path: first, last and a middle row of 6 experts
+    rng = np.random.default_rng(0)
+    y_rows = []
+    for ex in rng.choice(e, 6, replace=False):
+        a, b = int(first[ex]), int(first[ex + 1])
+        if b <= a:
+            continue
+        rows = sorted({a, b - 1, (a + b) // 2})
+        xin = xh[pr[rows] % t]
+        assert np.array_equal(buf.stages["expanded_seq_input"][rows].cpu().numpy().view(np.uint16), xin.view(np.uint16))
+        wg, wu, wd = (w[f"experts.{ex}.{j}.weight"].cpu().numpy() for j in range(3))
+        h = o.swiglu_fc1(xin, wg, wu)
+        ok, nbad, mx = o.check(buf.stages["expanded_fc1_output"][rows].cpu().numpy(), h, RTOL, ATOL)
+        assert ok, ("fc1", ex, nbad, mx)
+        y = o.linear_fp16(buf.stages["expanded_fc1_output"][rows].cpu().numpy(), wd)
+        ok, nbad, mx = o.check(buf.stages["expanded_fc2_output"][rows].cpu().numpy(), y, RTOL, ATOL)
+        assert ok, ("fc2", ex, nbad, mx)
+        y_rows.append(rows)
+    # sampled tokens of the shared expert and of the final combine
+    toks = [0, 1, 4097, t - 1]
+    sh1 = o.swiglu_fc1(xh[toks], w["shared_experts.0.weight"].cpu().numpy(), w["shared_experts.1.weight"].cpu().numpy())
+    ok, nbad, mx = o.check(buf.stages["shared_fc1_output"][toks].cpu().numpy(), sh1, RTOL, ATOL)
+    assert ok, ("shared fc1", nbad, mx)
+    sh2 = buf.stages["shared_fc2_output"][toks].cpu().numpy().astype(np.float32)
+    y_all = buf.stages["expanded_fc2_output"]
+    sm = got["expanded_seq_softmax"].astype(np.float32)
+    for j, tok in enumerate(toks):
+        pos = rev[np.arange(k) * t + tok]
+        acc = sh2[j] + (sm[pos][:, None] * y_all[pos].cpu().numpy().astype(np.float32)).sum(axis=0)
+        ok, nbad, mx = o.check(out[0, tok].cpu().numpy(), acc.astype(np.float16), RTOL, ATOL)
+        assert ok, ("combine", tok, nbad, mx)

@@ -1,0 +1,105 @@
+"""CPU tests: the numpy MoE oracle against fixtures made by the reference's own PyTorch ref_kernel."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from oracle import moe as o
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "moe_*.npz")))
+
+
+def load(path):
+    z = np.load(path)
+    d, f, e, ns, k, t, seed = [int(v) for v in z["cfg"]]
+    w = {n[2:]: z[n] for n in z.files if n.startswith("w:")}
+    return z, w, dict(d=d, f=f, e=e, ns=ns, k=k, t=t, seed=seed)
+
+
+def test_golden_files_present():
+    assert len(GOLDEN) >= 3
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_oracle_matches_reference_output(path):
+    z, w, c = load(path)
+    st = o.moe_stages(z["x"][0], w, c["e"], c["k"])
+    ok, nbad, mx = o.check(st["final_output"], z["ref_out"][0], rtol=1e-2, atol=1e-2)   # the reference's tolerance
+    assert ok, (nbad, mx)
+    ok, nbad, mx = o.check(st["final_output"], z["ref_out"][0], rtol=4e-3, atol=4e-3)   # and well inside it
+    assert ok, (nbad, mx)
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_topk_sets_match_reference_gate(path):
+    """Per-token expert SETS equal torch.topk(torch.softmax(..)) of the reference gate wherever the
+    k-th and (k+1)-th fp16 probabilities differ (ties have no contract in torch.topk)."""
+    z, w, c = load(path)
+    logits = o.router_logits(z["x"][0], w["router.weight"])
+    probs = o.softmax_fp16(logits).astype(np.float32)
+    idx, wts, _ = o.route(logits, c["k"])
+    srt = -np.sort(-probs, axis=1)
+    no_tie = (srt[:, c["k"] - 1] != srt[:, c["k"]]) if c["k"] < c["e"] else np.ones(len(srt), bool)
+    ours = np.sort(idx, axis=1)
+    ref = np.sort(z["ref_topk_idx"], axis=1)
+    assert np.array_equal(ours[no_tie], ref[no_tie])
+    assert no_tie.mean() > 0.9
+    # gate weights: same values up to one fp16 ulp of the probability
+    ref_w = np.take_along_axis(z["ref_topk_score"].astype(np.float32), np.argsort(z["ref_topk_idx"], axis=1), axis=1)
+    our_w = np.take_along_axis(wts.astype(np.float32), np.argsort(idx, axis=1), axis=1)
+    assert np.allclose(our_w[no_tie], ref_w[no_tie], rtol=2e-3, atol=1e-6)
+
+
+def test_det_exp_accuracy_and_range():
+    x = -np.linspace(0, 90, 20001).astype(np.float32)
+    e = o.det_exp(x)
+    ref = np.exp(np.maximum(x, -80).astype(np.float64))
+    assert np.max(np.abs(e / ref - 1)) < 4e-6
+    assert o.det_exp(np.float32(0.0)) == np.float32(1.0)
+    assert np.all(e > 0) and np.all(np.isfinite(e))
+
+
+def test_tie_rule_lowest_index_wins():
+    logits = np.zeros((3, 8), dtype=np.float16)
+    logits[1, [2, 5]] = 1.0           # two equal maxima -> 2 first, then 5, then 0
+    logits[2, 7] = -3.0
+    idx, w, src = o.route(logits, 3)
+    assert idx[0].tolist() == [0, 1, 2]
+    assert idx[1].tolist() == [2, 5, 0]
+    assert idx[2].tolist() == [0, 1, 2]
+    assert src.tolist() == [0, 3, 6, 1, 4, 7, 2, 5, 8]      # k_idx * T + t, token-major emission
+    assert w.dtype == np.float16 and np.all(np.diff(w.astype(np.float32), axis=1) <= 0)
+
+
+def test_row_sum_order_matches_lane_layout():
+    rng = np.random.default_rng(0)
+    for e in (4, 8, 32, 64, 256):
+        v = rng.random((5, e), dtype=np.float32)
+        s = o.det_row_sum(v)
+        assert np.allclose(s, v.sum(axis=1), rtol=1e-6)
+
+
+def test_permute_is_stable_and_inverse():
+    rng = np.random.default_rng(1)
+    t, k, e = 200, 4, 16
+    idx = rng.integers(0, e, (t, k)).astype(np.int32)
+    src = (np.arange(k)[None, :] * t + np.arange(t)[:, None]).reshape(-1).astype(np.int32)
+    pe, pr, first, rev = o.permute(idx, src, e)
+    assert np.all(np.diff(pe) >= 0)
+    assert first[0] == 0 and first[-1] == t * k
+    flat = idx.reshape(-1)
+    for ex in range(e):
+        seg = pr[first[ex]:first[ex + 1]]
+        # stable: original flat positions (t*k + i) ascending inside an expert
+        flat_pos = (seg % t) * k + seg // t
+        assert np.all(np.diff(flat_pos) > 0)
+        assert np.all(flat[flat_pos] == ex)
+    assert np.array_equal(pr[rev[src]], src)
+
+
+def test_empty_experts_get_empty_ranges():
+    idx = np.array([[0, 3], [3, 0]], dtype=np.int32)
+    src = np.array([0, 2, 1, 3], dtype=np.int32)
+    pe, pr, first, rev = o.permute(idx, src, 4)
+    assert first.tolist() == [0, 2, 2, 2, 4]
