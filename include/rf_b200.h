@@ -242,6 +242,49 @@ int rf_moe_combine(const void *expanded_fc2_output, const void *shared_fc2_outpu
                    const void *expanded_seq_softmax, int n_tokens, int top_k, int d_hidden, void *final_output,
                    rf_stream_t stream);
 
+/* ------------------------------------------------------- multi-GPU (one node) -- */
+/* None of these has a counterpart in the reference, which is single-GPU and has no collective
+ * call (grep for nccl|rccl|mpi under src/ is empty).  One process per GPU; buffers that peers
+ * touch are exported with CUDA IPC and addressed directly over NVLink.                        */
+
+/* cudaMalloc + cudaIpcGetMemHandle: a buffer other GPUs of the node may read and write.
+ * `handle64` receives the 64-byte IPC handle to send to the peers.                          */
+int rf_peer_alloc(size_t bytes, void **ptr, unsigned char *handle64);
+/* Maps a peer's buffer into this process (enables peer access on first use).                */
+int rf_peer_open(const unsigned char *handle64, void **ptr);
+int rf_peer_close(void *ptr);
+int rf_peer_free(void *ptr);
+
+/* N-split FP8 GEMM with the all-gather of C fused into the epilogue: this rank owns rows
+ * [rank*n/world, (rank+1)*n/world) of B and of its 128x128 scale blocks, computes that column
+ * slab of C and TMA-stores every tile into the full row-major C [m, n_total] of EVERY rank
+ * (`c_all[r]` = rank r's C as mapped in this process; c_all[rank] is local).  A and its scales
+ * are replicated.  n_total/world must be a multiple of 128.  Completion on all ranks needs a
+ * cross-rank barrier after the call (stream-ordered, e.g. a one-element NCCL all-reduce).     */
+int rf_fp8_gemm_nsplit(const void *a, const void *b_shard, const float *as, const float *bs_shard,
+                       void *const *c_all, int m, int n_total, int k, int rank, int world, rf_stream_t stream);
+
+/* Expert-parallel layout: from the all-gathered pair counts counts_all_dev [world][n_experts]
+ * computes, on the device, where this rank's rows land in the owners' receive buffers
+ * (send_base_dev [n_experts]) and the row ranges of this rank's own experts
+ * (recv_offsets_dev [n_experts/world + 1]).  Expert e lives on rank e / (n_experts/world).   */
+int rf_moe_ep_layout(const int *counts_all_dev, int rank, int world, int n_experts, int *send_base_dev,
+                     int *recv_offsets_dev, rf_stream_t stream);
+
+/* Dispatch: the token-row gather of expand_input (src/moe/moe_topk_kernel.cpp:174-213) writing
+ * directly into the owner ranks' receive buffers `recv_x_all[r]` (fp16 [capacity, d_hidden]).
+ * pair_rank / pair_row [n_pairs] record the destination of every locally sorted pair.         */
+int rf_moe_ep_dispatch(const void *x, const int *permuted_experts, const int *permuted_rows,
+                       const int *first_token_offset, const int *send_base, int n_tokens, int n_pairs, int d_hidden,
+                       int n_experts, int world, void *const *recv_x_all, int *pair_rank, int *pair_row,
+                       rf_stream_t stream);
+
+/* Combine: reduce_output (src/moe/moe_topk_kernel.cpp:215-251) reading each expert output row
+ * from its owner rank's `y_all[r]` (fp16 [capacity, d_hidden]) over NVLink.                   */
+int rf_moe_ep_combine(void *const *y_all, const void *shared_fc2_output, const int *rev_permuted_rows,
+                      const void *expanded_seq_softmax, const int *pair_rank, const int *pair_row, int n_tokens,
+                      int top_k, int d_hidden, int world, void *final_output, rf_stream_t stream);
+
 /* Library / build identification: "rf_b200 <version> sm_100a".               */
 const char *rf_version(void);
 

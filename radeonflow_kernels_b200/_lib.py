@@ -121,6 +121,25 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_moe_router_gemm.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp]
     L.rf_moe_combine.restype = ci
     L.rf_moe_combine.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, vp]
+    # ---- multi-GPU
+    pvp = ctypes.POINTER(vp)
+    pub = ctypes.POINTER(ctypes.c_ubyte)
+    L.rf_peer_alloc.restype = ci
+    L.rf_peer_alloc.argtypes = [sz, pvp, pub]
+    L.rf_peer_open.restype = ci
+    L.rf_peer_open.argtypes = [pub, pvp]
+    L.rf_peer_close.restype = ci
+    L.rf_peer_close.argtypes = [vp]
+    L.rf_peer_free.restype = ci
+    L.rf_peer_free.argtypes = [vp]
+    L.rf_fp8_gemm_nsplit.restype = ci
+    L.rf_fp8_gemm_nsplit.argtypes = [vp, vp, vp, vp, pvp, ci, ci, ci, ci, ci, vp]
+    L.rf_moe_ep_layout.restype = ci
+    L.rf_moe_ep_layout.argtypes = [vp, ci, ci, ci, vp, vp, vp]
+    L.rf_moe_ep_dispatch.restype = ci
+    L.rf_moe_ep_dispatch.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, pvp, vp, vp, vp]
+    L.rf_moe_ep_combine.restype = ci
+    L.rf_moe_ep_combine.argtypes = [pvp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, vp]
 
 
 def check(status: int, what: str) -> None:

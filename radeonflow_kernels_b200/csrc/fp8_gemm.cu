@@ -98,7 +98,7 @@ template <class Cfg>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                 const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_p,
-                const GemmParams p) {
+                const __grid_constant__ GemmDestMaps dests, const GemmParams p) {
     constexpr int BN = Cfg::kBN;
     constexpr int STAGES = Cfg::kStages;
     constexpr int CPT = Cfg::kColsPerThread;
@@ -326,7 +326,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_2d(&tma_c, slab, col0 + ch * 64, slab_row0);
+                            if (p.n_dest <= 1) {
+                                tma_store_2d(&tma_c, slab, col0 + ch * 64, slab_row0);
+                            } else {
+                                // N-split GEMM: the slab goes to every GPU's C (own memory and peers over
+                                // NVLink), which is the all-gather of C done by the epilogue itself
+                                for (int dd = 0; dd < p.n_dest; ++dd)
+                                    tma_store_2d(&dests.m[dd], slab, p.c_col_offset + col0 + ch * 64, slab_row0);
+                            }
                             tma_store_commit();
                         }
                     }
@@ -393,7 +400,8 @@ using Cfg256 = GemmCfg<256, 4>;
 
 template <class Cfg>
 cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
-                       const CUtensorMap& tma_p, const GemmParams& p, int num_sms, cudaStream_t stream) {
+                       const CUtensorMap& tma_p, const GemmDestMaps& dests, const GemmParams& p, int num_sms,
+                       cudaStream_t stream) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -405,7 +413,7 @@ cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const
     }
     const int total = p.tiles_m * p.tiles_n * p.splits;
     const int grid = total < num_sms ? total : num_sms;
-    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tma_a, tma_b, tma_c, tma_p, p);
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tma_a, tma_b, tma_c, tma_p, dests, p);
     return cudaGetLastError();
 }
 
@@ -423,10 +431,15 @@ extern "C" void rf_debug_wait_stats(unsigned long long* out8, int reset) {
 #endif
 
 cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
-                            const CUtensorMap& tma_p, const GemmParams& p, int block_n, int num_sms,
-                            cudaStream_t stream) {
-    cudaError_t e = block_n == 256 ? launch_cfg<Cfg256>(tma_a, tma_b, tma_c, tma_p, p, num_sms, stream)
-                                   : launch_cfg<Cfg128>(tma_a, tma_b, tma_c, tma_p, p, num_sms, stream);
+                            const CUtensorMap& tma_p, const GemmDestMaps* dests, const GemmParams& p, int block_n,
+                            int num_sms, cudaStream_t stream) {
+    GemmDestMaps local;
+    if (!dests) {
+        for (int i = 0; i < 8; ++i) local.m[i] = tma_c;
+        dests = &local;
+    }
+    cudaError_t e = block_n == 256 ? launch_cfg<Cfg256>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
+                                   : launch_cfg<Cfg128>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream);
     if (e != cudaSuccess) return e;
     if (p.splits > 1) {
         const size_t mn = (size_t)p.m * p.n;

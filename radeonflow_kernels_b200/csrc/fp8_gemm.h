@@ -15,14 +15,22 @@ struct GemmParams {
     int* status;            // device status word (0 = ok)
     int m, n, k;
     int tiles_m, tiles_n, splits;
+    int n_dest;             // copies of C to write (1, or the number of GPUs of an N-split GEMM)
+    int c_col_offset;       // column of this GEMM's C inside each destination matrix
+};
+
+// Output tensor maps of an N-split GEMM: entry d addresses GPU d's full row-major C.
+struct GemmDestMaps {
+    CUtensorMap m[8];
 };
 
 // Launches the GEMM (and the split-K fix-up when p.splits > 1) on `stream`.
 // `block_n` is the tile width the tensor map of B and p.tiles_n were built for: 128 or 256.
 // `tma_c` stores bf16 C boxes of 32 rows x 64 columns; `tma_p` (used when p.splits > 1) stores fp32
 // slice boxes of 32 rows x 32 columns into the [splits][m][n] scratch.
+// When p.n_dest > 1, `dests` holds p.n_dest maps and replaces tma_c (split-K is not combined with it).
 cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
-                            const CUtensorMap& tma_p, const GemmParams& p, int block_n, int num_sms,
-                            cudaStream_t stream);
+                            const CUtensorMap& tma_p, const GemmDestMaps* dests, const GemmParams& p, int block_n,
+                            int num_sms, cudaStream_t stream);
 
 }  // namespace rf

@@ -65,9 +65,20 @@ GemmPlan choose_plan(int m, int n, int k, int num_sms, int forced_split) {
     return p256.cost <= p128.cost * 1.02 ? p256 : p128;
 }
 
+// `dest_c` / `n_dest` / `dest_n` / `col_offset`: when n_dest > 1 the [m, n] result is written at column
+// `col_offset` of each of the n_dest row-major [m, dest_n] matrices in dest_c (N-split GEMM) and `c` is unused.
 int gemm_impl(const void* a, const void* b, const float* as, const float* bs, void* c, int m, int n, int k,
-              int split_k, void* workspace, size_t workspace_bytes, bool own_workspace, cudaStream_t stream) {
+              int split_k, void* workspace, size_t workspace_bytes, bool own_workspace, cudaStream_t stream,
+              void* const* dest_c = nullptr, int n_dest = 1, int dest_n = 0, int col_offset = 0) {
     if (!shape_ok(m, n, k)) return RF_ERR_BAD_SHAPE;
+    if (n_dest > 1) {
+        if (!dest_c || n_dest > 8 || dest_n < col_offset + n || dest_n % 8 != 0 || col_offset % 64 != 0)
+            return RF_ERR_BAD_SHAPE;
+        for (int i = 0; i < n_dest; ++i)
+            if (!dest_c[i] || ((uintptr_t)dest_c[i] & 15)) return RF_ERR_NULL_POINTER;
+        c = dest_c[0];
+        split_k = 1;
+    }
     if (!a || !b || !as || !bs || !c) return RF_ERR_NULL_POINTER;
     if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) return RF_ERR_MISALIGNED;
     if (((uintptr_t)as | (uintptr_t)bs) & 3) return RF_ERR_MISALIGNED;
@@ -123,7 +134,18 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     p.tiles_m = (m + 127) / 128;
     p.tiles_n = (n + bn - 1) / bn;
     p.splits = splits;
-    cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, p, bn, st->num_sms, stream);
+    p.n_dest = n_dest;
+    p.c_col_offset = col_offset;
+    rf::GemmDestMaps dests;
+    if (n_dest > 1) {
+        for (int i = 0; i < 8; ++i) {
+            void* base = dest_c[i < n_dest ? i : 0];
+            if (!rf::encode_tma_2d(&dests.m[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, (uint64_t)m,
+                                   (uint64_t)dest_n, (uint64_t)dest_n * 2, 32, 64, true))
+                return RF_ERR_CUDA;
+        }
+    }
+    cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, n_dest > 1 ? &dests : nullptr, p, bn, st->num_sms, stream);
     if (e != cudaSuccess) {
         fprintf(stderr, "rf_b200: fp8 gemm launch failed: %s\n", cudaGetErrorString(e));
         return RF_ERR_CUDA;
@@ -170,6 +192,19 @@ int rf_fp8_gemm(const void* a, const void* b, const float* as, const float* bs, 
                 int split_k, void* workspace, size_t workspace_bytes, rf_stream_t stream) {
     return gemm_impl(a, b, as, bs, c, m, n, k, split_k, workspace, workspace_bytes, false,
                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int rf_fp8_gemm_nsplit(const void* a, const void* b_shard, const float* as, const float* bs_shard,
+                       void* const* c_all, int m, int n_total, int k, int rank, int world, rf_stream_t stream) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || n_total % world != 0) return RF_ERR_BAD_SHAPE;
+    const int n_loc = n_total / world;
+    if (n_loc % 128 != 0) return RF_ERR_BAD_SHAPE;     // shards must keep whole 128-wide scale blocks
+    if (!c_all) return RF_ERR_NULL_POINTER;
+    if (world == 1)
+        return gemm_impl(a, b_shard, as, bs_shard, c_all[0], m, n_total, k, 1, nullptr, 0, true,
+                         reinterpret_cast<cudaStream_t>(stream));
+    return gemm_impl(a, b_shard, as, bs_shard, nullptr, m, n_loc, k, 1, nullptr, 0, true,
+                     reinterpret_cast<cudaStream_t>(stream), c_all, world, n_total, rank * n_loc);
 }
 
 void run(void* a, void* b, void* as, void* bs, void* c, int m, int n, int k, PerfMetrics* metrics,

@@ -1,0 +1,142 @@
+// Expert-parallel token exchange over NVLink peer memory.  The reference is single-GPU; these kernels
+// are the multi-GPU form of its expand_input / reduce_output pair (src/moe/moe_topk_kernel.cpp:174-251):
+// the row gather writes straight into the owner GPU's receive buffer (dispatch) and the weighted
+// combine reads the expert outputs straight from the owner GPUs (combine).  Only ordinary peer
+// loads and stores are used; ordering between GPUs comes from stream-ordered barriers outside.
+#include "moe_kernels.h"
+
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace rf {
+
+namespace {
+
+__global__ void __launch_bounds__(1024)
+ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_experts, int* __restrict__ send_base,
+                 int* __restrict__ recv_offsets) {
+    __shared__ int tot[1024];
+    const int e = threadIdx.x;
+    const int per = n_experts / world;
+    int t = 0, before_me = 0;
+    if (e < n_experts) {
+        for (int s = 0; s < world; ++s) {
+            const int c = counts_all[s * n_experts + e];
+            if (s < rank) before_me += c;
+            t += c;
+        }
+        tot[e] = t;
+    }
+    __syncthreads();
+    if (e < n_experts) {
+        const int owner_first = (e / per) * per;
+        int base = 0;
+        for (int j = owner_first; j < e; ++j) base += tot[j];
+        send_base[e] = base + before_me;
+    }
+    if (e <= per) {
+        int off = 0;
+        for (int j = 0; j < e; ++j) off += tot[rank * per + j];
+        recv_offsets[e] = off;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted_experts,
+                   const int* __restrict__ permuted_rows, const int* __restrict__ first_token_offset,
+                   const int* __restrict__ send_base, int n_tokens, int n_pairs, int vec_per_row,
+                   int experts_per_rank, PeerPtrs recv_x, int* __restrict__ pair_rank, int* __restrict__ pair_row) {
+    const size_t total = (size_t)n_pairs * vec_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int p = (int)(i / vec_per_row);
+        const int v = (int)(i - (size_t)p * vec_per_row);
+        const int e = permuted_experts[p];
+        const int q = e / experts_per_rank;
+        const int row = send_base[e] + (p - first_token_offset[e]);
+        const int tok = permuted_rows[p] % n_tokens;
+        uint4* dst = static_cast<uint4*>(recv_x.p[q]) + (size_t)row * vec_per_row + v;
+        *dst = __ldg(x + (size_t)tok * vec_per_row + v);
+        if (v == 0) {
+            pair_rank[p] = q;
+            pair_row[p] = row;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+ep_combine_kernel(PeerPtrs y, const uint4* __restrict__ shared_out, const int* __restrict__ rev,
+                  const __half* __restrict__ weights, const int* __restrict__ pair_rank,
+                  const int* __restrict__ pair_row, int n_tokens, int top_k, int vec_per_row, uint4* __restrict__ out) {
+    const int t = blockIdx.x;
+    __shared__ const uint4* src_s[8];
+    __shared__ float w_s[8];
+    if (threadIdx.x < top_k) {
+        const int p = rev[threadIdx.x * n_tokens + t];
+        src_s[threadIdx.x] = static_cast<const uint4*>(y.p[pair_rank[p]]) + (size_t)pair_row[p] * vec_per_row;
+        w_s[threadIdx.x] = __half2float(weights[p]);
+    }
+    __syncthreads();
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int i = 0; i < top_k; ++i) {
+            const uint4 q = src_s[i][v];            // peer (or local) load
+            const __half2* h = reinterpret_cast<const __half2*>(&q);
+            const float w = w_s[i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                acc[2 * j] = fmaf(w, f.x, acc[2 * j]);
+                acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
+            }
+        }
+        const uint4 sq = __ldg(shared_out + (size_t)t * vec_per_row + v);
+        const __half2* sh = reinterpret_cast<const __half2*>(&sq);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(sh[j]);
+            oh[j] = __floats2half2_rn(acc[2 * j] + f.x, acc[2 * j + 1] + f.y);
+        }
+        out[(size_t)t * vec_per_row + v] = o;
+    }
+}
+
+}  // namespace
+
+cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int n_experts, int* send_base,
+                                 int* recv_offsets, cudaStream_t stream) {
+    ep_layout_kernel<<<1, 1024, 0, stream>>>(counts_all, rank, world, n_experts, send_base, recv_offsets);
+    return cudaGetLastError();
+}
+
+cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, const int* permuted_rows,
+                                   const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs,
+                                   int row_bytes, int experts_per_rank, const PeerPtrs& recv_x, int* pair_rank,
+                                   int* pair_row, int num_sms, cudaStream_t stream) {
+    const int vec = row_bytes / 16;
+    const size_t total = (size_t)n_pairs * vec;
+    if (total == 0) return cudaSuccess;
+    size_t blocks = (total + 255) / 256;
+    const size_t cap = (size_t)num_sms * 16;
+    if (blocks > cap) blocks = cap;
+    ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(x), permuted_experts,
+                                                             permuted_rows, first_token_offset, send_base, n_tokens,
+                                                             n_pairs, vec, experts_per_rank, recv_x, pair_rank,
+                                                             pair_row);
+    return cudaGetLastError();
+}
+
+cudaError_t moe_ep_combine_launch(const PeerPtrs& y, const void* shared_out, const int* rev, const void* weights,
+                                  const int* pair_rank, const int* pair_row, int n_tokens, int top_k, int row_bytes,
+                                  void* out, cudaStream_t stream) {
+    if (n_tokens == 0) return cudaSuccess;
+    ep_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, static_cast<const uint4*>(shared_out), rev,
+                                                    static_cast<const __half*>(weights), pair_rank, pair_row,
+                                                    n_tokens, top_k, row_bytes / 16, static_cast<uint4*>(out));
+    return cudaGetLastError();
+}
+
+}  // namespace rf

@@ -22,6 +22,26 @@ cudaError_t moe_set_range_launch(int* dst, int a, int b, cudaStream_t stream);
 cudaError_t moe_tile_list_launch(const int* offsets, int n_groups, int* tile_group, int* tile_row0, int* tile_count,
                                  cudaStream_t stream);
 
+// ---- expert-parallel exchange over peer memory (moe_ep.cu)
+struct PeerPtrs {
+    void* p[8];
+};
+// counts_all [world][n_experts] (row s = pairs per global expert on source rank s).  Writes
+//   send_base[e]      row, inside the owner rank's receive buffer, of this rank's first pair for expert e
+//   recv_offsets[j]   j = 0..n_experts/world: row range of local expert j in this rank's receive buffer
+cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int n_experts, int* send_base,
+                                 int* recv_offsets, cudaStream_t stream);
+// Copies the token row of every local (token, expert) pair into the owner rank's receive buffer
+// (peer stores) and records where it went (pair_rank, pair_row).
+cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, const int* permuted_rows,
+                                   const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs,
+                                   int row_bytes, int experts_per_rank, const PeerPtrs& recv_x, int* pair_rank,
+                                   int* pair_row, int num_sms, cudaStream_t stream);
+// out[t] = fp16(sum_i w_i * Y_{rank_i}[row_i] + shared[t]) with Y rows read from the owner ranks (peer loads).
+cudaError_t moe_ep_combine_launch(const PeerPtrs& y, const void* shared_out, const int* rev, const void* weights,
+                                  const int* pair_rank, const int* pair_row, int n_tokens, int top_k, int row_bytes,
+                                  void* out, cudaStream_t stream);
+
 // ---- grouped fp16 GEMM (moe_gemm.cu)
 enum MoeGemmMode {
     kMoeGemmPlain = 0,    // out[r, n] = fp16(X[r,:] . W_g[:, n]); W_g is [K, N] row-major (N contiguous)

@@ -1,0 +1,136 @@
+"""Multi-GPU paths.  CPU part: two gloo ranks exercise the expert-parallel exchange protocol (count
+all-gather, host-side layout planner, row exchange) against the single-process oracle.  GPU part:
+torch.distributed.run launches tests/mgpu_worker.py with one rank per visible GPU (one is enough to
+run the peer-memory code path; more exercise NVLink)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+GLOO_WORKER = r'''
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["RF_ROOT"])
+from oracle import moe as om
+from radeonflow_kernels_b200.multi_gpu import ep_layout_reference
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")
+d, f, E, K, T_loc = 64, 64, 8, 2, 40
+T = T_loc * world
+x, w, cfg = om.generate_input(d, f, E, 1, K, T, 99)
+bias = om.zipf_router_bias(E, 1.1, 3)
+e_loc = E // world
+x_loc = x[0, rank * T_loc:(rank + 1) * T_loc]
+# local routing and local stable sort by GLOBAL expert id
+logits = om.router_logits(x_loc, w["router.weight"], bias)
+idx, gw, src = om.route(logits, K)
+pe, pr, first, rev = om.permute(idx, src, E)
+counts = torch.from_numpy(np.diff(first).astype(np.int32))
+gathered = [torch.zeros_like(counts) for _ in range(world)]
+dist.all_gather(gathered, counts)
+counts_all = np.stack([g.numpy() for g in gathered])
+send_base, recv_off = ep_layout_reference(counts_all, rank)
+# dispatch: rows for owner q form a contiguous run of the local sorted order
+rows = torch.from_numpy(x_loc[pr % T_loc].astype(np.float32))
+dest_row = send_base[pe] + (np.arange(len(pe)) - first[pe])
+owner = pe // e_loc
+cap = int(counts_all.sum())
+recv = torch.zeros((cap, d))
+for q in range(world):            # emulate the peer stores with point-to-point sends
+    sel = np.nonzero(owner == q)[0]
+    payload = torch.cat([torch.from_numpy(dest_row[sel].astype(np.float32))[:, None], rows[sel]], dim=1)
+    sizes = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(sizes, torch.tensor([len(sel)], dtype=torch.int64))
+    if q == rank:
+        for s in range(world):
+            n = int(sizes[s])
+            buf = payload if s == rank else torch.zeros((n, d + 1))
+            if s != rank and n:
+                dist.recv(buf, src=s)
+            if n:
+                recv[buf[:, 0].long()] = buf[:, 1:]
+    elif len(sel):
+        dist.send(payload, dst=q)
+# experts on the received rows
+recv16 = recv.numpy().astype(np.float16)
+y = np.zeros((cap, d), dtype=np.float16)
+for j in range(e_loc):
+    a, b = int(recv_off[j]), int(recv_off[j + 1])
+    e = rank * e_loc + j
+    if b > a:
+        h = om.swiglu_fc1(recv16[a:b], w[f"experts.{e}.0.weight"], w[f"experts.{e}.1.weight"])
+        y[a:b] = om.linear_fp16(h, w[f"experts.{e}.2.weight"])
+assert int(recv_off[-1]) == int(counts_all[:, rank * e_loc:(rank + 1) * e_loc].sum())
+# combine: pull rows back (emulated by gathering every rank's y)
+ys = [torch.zeros((int(counts_all[:, q * e_loc:(q + 1) * e_loc].sum()), d)) for q in range(world)]
+for q in range(world):
+    t = torch.from_numpy(y[: ys[q].shape[0]].astype(np.float32)) if q == rank else ys[q]
+    dist.broadcast(t, src=q)
+    ys[q] = t
+sh = om.linear_fp16(om.swiglu_fc1(x_loc, w["shared_experts.0.weight"], w["shared_experts.1.weight"]),
+                    w["shared_experts.2.weight"]).astype(np.float32)
+wts = gw[pr % T_loc, pr // T_loc].astype(np.float32)
+out = sh.copy()
+for i in range(K):
+    p = rev[i * T_loc + np.arange(T_loc)]
+    yrow = np.stack([ys[owner[pp]][dest_row[pp]].numpy() for pp in p])
+    out += wts[p][:, None] * yrow
+ref = om.moe_stages(x[0], w, E, K, router_bias=bias)["final_output"][rank * T_loc:(rank + 1) * T_loc]
+ok, nbad, mx = om.check(out.astype(np.float16), ref)
+assert ok, (nbad, mx)
+print("GLOO OK", rank)
+'''
+
+
+def test_expert_parallel_protocol_two_gloo_ranks(tmp_path):
+    script = tmp_path / "gloo_worker.py"
+    script.write_text(GLOO_WORKER)
+    env = dict(os.environ, RF_ROOT=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE="2",
+               OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"GLOO OK {r}" in o, o[-2000:]
+
+
+def test_layout_planner_small_case():
+    from radeonflow_kernels_b200.multi_gpu import ep_layout_reference
+    counts = np.array([[1, 2, 0, 3], [4, 0, 5, 6]])        # 2 ranks, 4 experts (2 per rank)
+    sb0, ro0 = ep_layout_reference(counts, 0)
+    sb1, ro1 = ep_layout_reference(counts, 1)
+    # owner 0 holds experts 0,1: rows [e0: r0(1) r1(4)] [e1: r0(2) r1(0)]
+    assert sb0.tolist() == [0, 5, 0, 5] and sb1.tolist() == [1, 7, 0, 8]
+    assert ro0.tolist() == [0, 5, 7] and ro1.tolist() == [0, 5, 14]
+
+
+@pytest.mark.gpu
+def test_multi_gpu_worker_all_visible_gpus():
+    import torch
+    n = min(torch.cuda.device_count(), 8)
+    assert n >= 1
+    while n & (n - 1):
+        n -= 1
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "mgpu_worker.py")]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    out = res.stdout + res.stderr
+    assert res.returncode == 0, out[-4000:]
+    for r in range(n):
+        assert f"MGPU OK rank={r}" in out, out[-4000:]
