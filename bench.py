@@ -195,6 +195,164 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+
+# ------------------------------------------------------------------------- extra workloads --
+def _timed(fn, iters, warm, dev, world, dist):
+    """Device time per iteration (ms): CUDA events on the current stream, barrier + synchronize on
+    both sides, max over ranks."""
+    import torch
+    for _ in range(warm):
+        fn()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def moe_layer_flops(t, d, f, e, k):
+    return 2.0 * t * d * e + 2.0 * t * k * 3 * d * f + 2.0 * t * 3 * d * f
+
+
+def make_moe_weights(torch, dev, d, f, experts, seed, with_router_for=None):
+    """Random-init weights with the reference generator's scales (scripts/problems/moe/reference.py:192-238),
+    drawn on the device.  `experts` = list of local expert ids (names are local: experts.0...)."""
+    g = torch.Generator(device=dev)
+    w = {}
+    g.manual_seed(seed)
+    e_total = with_router_for
+    w["router.weight"] = (torch.randn((e_total, d), device=dev, generator=g) / d ** 0.5).half()
+    for j, shape, sc in ((0, (d, f), f), (1, (d, f), f), (2, (f, d), d)):
+        w[f"shared_experts.{j}.weight"] = (torch.randn(shape, device=dev, generator=g) / sc ** 0.5).half()
+    for j, e in enumerate(experts):
+        g.manual_seed(seed * 1000 + e)
+        w[f"experts.{j}.0.weight"] = (torch.randn((d, f), device=dev, generator=g) / f ** 0.5).half()
+        w[f"experts.{j}.1.weight"] = (torch.randn((d, f), device=dev, generator=g) / f ** 0.5).half()
+        w[f"experts.{j}.2.weight"] = (torch.randn((f, d), device=dev, generator=g) / d ** 0.5).half()
+    return w
+
+
+def run_extras(args, rank, world, dev, dist, peaks):
+    """MoE layer tokens/s (single-GPU config and the expert-parallel config) and the N-split GEMM."""
+    import torch
+    from oracle import moe as om     # only for the seeded Zipf bias (input generation)
+    from radeonflow_kernels_b200 import moe as M, multi_gpu as mg
+    out = {}
+    f16_peak = peaks["bf16_tflops"]
+
+    # ---- config 3: single-GPU MoE layer, T=8192, d=7168, f=2048, E=32, top-4 (every rank runs a replica)
+    d, f, e, k, t = 7168, 2048, 32, 4, 8192
+    w = make_moe_weights(torch, dev, d, f, list(range(e)), 11, with_router_for=e)
+    cfg = {"d_hidden": d, "d_expert": f, "n_routed_experts": e, "n_shared_experts": 1, "n_experts_per_token": k,
+           "batch_size": 1, "seq_len": t}
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    x = torch.randn((1, t, d), device=dev, dtype=torch.float16, generator=g)
+    buf = M.MoEBuffers(x, w, cfg)
+    L = _lib_handle()
+    sp = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ms = _timed(lambda: L.rf_moe_forward(ctypes.byref(buf.raw), None, sp, None), 10, 3, dev, world, dist)
+    fl = moe_layer_flops(t, d, f, e, k)
+    out["moe_single_gpu"] = {
+        "config": "T=8192 d=7168 f=2048 E=32 top-4 + 1 shared, fp16, router GEMM included",
+        "ms_per_layer": ms, "tokens_per_s": world * t / (ms * 1e-3), "tflops_per_gpu": fl / (ms * 1e-3) / 1e12,
+        "frac_f16_peak": fl / (ms * 1e-3) / 1e12 / f16_peak, "parallelism": "replicas" if world > 1 else "single"}
+    del buf, w, x
+    torch.cuda.empty_cache()
+
+    # ---- config 4: expert-parallel MoE, 32768 tokens in total, E=256 top-8, Zipf(1.1)-skewed routing
+    d, f, e, k, t_total = 7168, 2048, 256, 8, 32768
+    t_loc = t_total // world
+    e_loc = e // world
+    # Static load-aware placement decided before the timed region: one calibration pass of the router
+    # and top-k kernels over this run's tokens gives pairs per expert; experts are then renumbered in
+    # placement order (router rows and bias permuted), which leaves the layer itself unchanged.
+    bias_np = om.zipf_router_bias(e, 1.1, 17)
+    g.manual_seed(100 + rank)
+    x = torch.randn((t_loc, d), device=dev, dtype=torch.float16, generator=g)
+    g.manual_seed(13)
+    router_w = (torch.randn((e, d), device=dev, generator=g) / d ** 0.5).half()
+    cal_scores = torch.empty((t_loc, e), dtype=torch.float16, device=dev)
+    cal_idx = torch.empty((t_loc, k), dtype=torch.int32, device=dev)
+    cal_w = torch.empty((t_loc, k), dtype=torch.float16, device=dev)
+    cal_src = torch.empty((t_loc * k,), dtype=torch.int32, device=dev)
+    bias0 = torch.from_numpy(bias_np).to(dev)
+    L.rf_moe_router_gemm(x.data_ptr(), router_w.data_ptr(), bias0.data_ptr(), t_loc, e, d, cal_scores.data_ptr(), sp)
+    L.rf_moe_topk(cal_scores.data_ptr(), t_loc, e, k, cal_idx.data_ptr(), cal_w.data_ptr(), cal_src.data_ptr(), sp)
+    loads = torch.bincount(cal_idx.reshape(-1).long(), minlength=e).double()
+    if world > 1:
+        dist.all_reduce(loads)
+    order = mg.balanced_expert_placement(loads.cpu().numpy(), world)
+    w = make_moe_weights(torch, dev, d, f, [int(order[rank * e_loc + j]) for j in range(e_loc)], 13,
+                         with_router_for=e)
+    w["router.weight"] = router_w[torch.from_numpy(order).to(dev)].contiguous()
+    cfg = {"d_hidden": d, "d_expert": f, "n_routed_experts": e, "n_shared_experts": 1, "n_experts_per_token": k,
+           "batch_size": 1, "seq_len": t_loc}
+    bias = torch.from_numpy(bias_np[order]).to(dev)
+    layer = mg.ExpertParallelMoE(cfg, w, t_loc, dev, router_bias=bias)
+    ms = _timed(lambda: layer.forward(x), 5, 2, dev, world, dist)
+    rows = torch.tensor([float(layer.received_rows())], dtype=torch.float64, device=dev)
+    mx, sm = rows.clone(), rows.clone()
+    if world > 1:
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    fl = moe_layer_flops(t_total, d, f, e, k)
+    out["moe_expert_parallel"] = {
+        "config": "32768 tokens, d=7168 f=2048 E=256 top-8 + 1 shared, Zipf(1.1) router bias, experts sharded "
+                  "E/N per GPU, dispatch by peer stores, combine by peer loads",
+        "ms_per_layer": ms, "tokens_per_s": t_total / (ms * 1e-3), "tflops_total": fl / (ms * 1e-3) / 1e12,
+        "scaling": "strong", "rows_per_gpu_max": mx.item(), "rows_per_gpu_mean": sm.item() / world,
+        "imbalance_max_over_mean": mx.item() / (sm.item() / world)}
+    layer.close()
+    del layer, w, x
+    torch.cuda.empty_cache()
+
+    # ---- config 2: M=16384 N=28672 K=7168 split along N, C assembled on every GPU by the epilogue
+    m, n, kk = 16384, 28672, 7168
+    n_loc = n // world
+    g.manual_seed(7)
+    a = torch.randn((m, kk), device=dev, generator=g).clamp_(-240, 240).to(torch.float8_e4m3fn)
+    a_s = ((0.5 + 1.5 * torch.rand((m, kk // 128), device=dev, generator=g)) * 2.0 ** -7).float()
+    g.manual_seed(70 + rank)
+    b = torch.randn((n_loc, kk), device=dev, generator=g).clamp_(-240, 240).to(torch.float8_e4m3fn)
+    b_s = ((0.5 + 1.5 * torch.rand((n_loc // 128, kk // 128), device=dev, generator=g)) * 2.0 ** -7).float()
+    cbuf = mg.PeerBuffer(m * n * 2, dev)
+    flag = torch.zeros(1, device=dev)
+
+    def step():
+        mg.fp8_gemm_nsplit(a, b, a_s, b_s, cbuf, m, n, kk)
+        mg.stream_barrier(flag)
+    ms = _timed(step, 5, 2, dev, world, dist)
+    c_loc = torch.empty((m, n_loc), dtype=torch.bfloat16, device=dev)
+    ms_local = _timed(lambda: L.rf_fp8_gemm(a.data_ptr(), b.data_ptr(), a_s.data_ptr(), b_s.data_ptr(),
+                                            c_loc.data_ptr(), m, n_loc, kk, 1, None, 0, sp), 5, 2, dev, world, dist)
+    fl = 2.0 * m * n * kk
+    nv_bytes = (world - 1) / world * m * n * 2          # C bytes each GPU receives over NVLink
+    out["gemm_nsplit"] = {
+        "config": "M=16384 N=28672 K=7168 fp8, B row-partitioned, bf16 C all-gathered by epilogue peer stores",
+        "ms": ms, "tflops_total": fl / (ms * 1e-3) / 1e12, "ms_gemm_only_local_c": ms_local,
+        "tflops_total_gemm_only": fl / (ms_local * 1e-3) / 1e12, "scaling": "strong",
+        "nvlink_bytes_in_per_gpu": nv_bytes,
+        "roofline_ms": max(fl / world / (2 * peaks["bf16_tflops"] * 1e12), nv_bytes / 770e9) * 1e3}
+    cbuf.close()
+    return out
+
+
+def _lib_handle():
+    from radeonflow_kernels_b200 import _lib
+    return _lib.lib()
+
 # ------------------------------------------------------------------------------------ GPU arm --
 def run_gpu_arm(args):
     import torch
@@ -369,6 +527,12 @@ def run_gpu_arm(args):
     e2e_ms = float(t2.item()) / e2e_steps
     e2e_val = world * step_flops / (e2e_ms * 1e-3) / 1e12
 
+    extras = None
+    if not args.no_extras:
+        del host
+        torch.cuda.empty_cache()
+        extras = run_extras(args, rank, world, dev, dist, peaks)
+
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
@@ -404,6 +568,7 @@ def run_gpu_arm(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "shapes": per_shape,
+            "extras": extras,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -413,14 +578,18 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the MoE and N-split GEMM workloads")
     ap.add_argument("--shapes", default="", help="restrict the sweep, e.g. 6144x4608x7168,1024x512x7168 "
                                                  "(profiling aid; the JSON line names the restricted workload)")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 200 if args.impl == "b200" else 10
     if args.shapes:
+        args.no_extras = True
         global SWEEP
         SWEEP = [tuple(int(v) for v in t.split("x")) for t in args.shapes.split(",")]
     if args.impl == "reference":

@@ -40,6 +40,27 @@ def ep_layout_reference(counts_all: np.ndarray, rank: int):
     return send_base.astype(np.int32), recv.astype(np.int32)
 
 
+def balanced_expert_placement(loads: np.ndarray, world: int) -> np.ndarray:
+    """Static load-aware expert placement (greedy longest-processing-time): experts, heaviest first,
+    go to the rank with the least load that still has a free slot (E/world slots per rank).
+
+    `loads` [E]: pairs per expert observed on a calibration batch (or any popularity estimate).
+    Returns `order` with order[r * E/world + j] = original id of rank r's j-th expert.  Renumbering
+    the experts in this order (router rows, bias entries, weight list) leaves the layer unchanged
+    while the owner of new id e' stays e' // (E/world), which is what the exchange kernels assume.
+    """
+    loads = np.asarray(loads, dtype=np.float64)
+    n = loads.size
+    per = n // world
+    tot = np.zeros(world)
+    slots = [[] for _ in range(world)]
+    for e in np.argsort(-loads, kind="stable"):
+        r = min((r for r in range(world) if len(slots[r]) < per), key=lambda r: (tot[r], r))
+        slots[r].append(int(e))
+        tot[r] += loads[e]
+    return np.array([e for r in range(world) for e in slots[r]], dtype=np.int64)
+
+
 # ------------------------------------------------------------------------------- peer buffers --
 class _RawCuda:
     """Adapter so torch can view a raw device allocation without copying."""
@@ -185,6 +206,9 @@ class ExpertParallelMoE:
         self.flag = torch.zeros(1, dtype=torch.float32, device=dev)
         L = _lib.lib()
         self.sort_scratch = e((max(16, L.rf_moe_permute_scratch_bytes(T * K, E)),), torch.uint8)
+        self.side_stream = torch.cuda.Stream(device=dev)
+        self.ev_ready = torch.cuda.Event()
+        self.ev_sent = torch.cuda.Event()
         self.recv_x = PeerBuffer(self.capacity * d * 2, dev, group)
         self.y = PeerBuffer(self.capacity * d * 2, dev, group)
 
@@ -221,15 +245,23 @@ class ExpertParallelMoE:
             self.counts_all.copy_(counts)
         chk(L.rf_moe_ep_layout(self.counts_all.data_ptr(), self.rank, self.world, E, self.send_base.data_ptr(),
                                self.recv_offsets.data_ptr(), s), "rf_moe_ep_layout")
+        # Dispatch runs on a side stream; the shared expert, which needs no exchange, runs on the main
+        # stream at the same time (the copy kernel's blocks need no shared memory and co-reside with
+        # the GEMM's CTAs), hiding the NVLink transfer.
+        main = torch.cuda.current_stream()
+        self.ev_ready.record(main)
+        self.side_stream.wait_event(self.ev_ready)
+        side = ctypes.c_void_p(self.side_stream.cuda_stream)
         chk(L.rf_moe_ep_dispatch(x.data_ptr(), self.perm_experts.data_ptr(), self.perm_rows.data_ptr(),
                                  self.first.data_ptr(), self.send_base.data_ptr(), T, T * K, d, E, self.world,
-                                 self.recv_x.ptr_array, self.pair_rank.data_ptr(), self.pair_row.data_ptr(), s),
+                                 self.recv_x.ptr_array, self.pair_rank.data_ptr(), self.pair_row.data_ptr(), side),
             "rf_moe_ep_dispatch")
-        # the shared expert needs no exchange: it runs while the peers' dispatch stores are in flight
+        self.ev_sent.record(self.side_stream)
         chk(L.rf_moe_grouped_gemm(x.data_ptr(), T, self._s_gate, self._s_up, self.single_offsets.data_ptr(), 1,
                                   self.fs, d, self.sh1.data_ptr(), s), "shared fc1")
         chk(L.rf_moe_grouped_gemm(self.sh1.data_ptr(), T, self._s_down, None, self.single_offsets.data_ptr(), 1, d,
                                   self.fs, self.sh2.data_ptr(), s), "shared fc2")
+        main.wait_event(self.ev_sent)
         stream_barrier(self.flag, self.group)          # every rank's dispatch has landed
         chk(L.rf_moe_grouped_gemm(self.recv_x.local_ptr, self.capacity, self._w_gate, self._w_up,
                                   self.recv_offsets.data_ptr(), self.E_loc, f, d, self.h.data_ptr(), s), "routed fc1")
