@@ -80,6 +80,31 @@ size_t rf_fp8_gemm_workspace_bytes(int m, int n, int k, int split_k);
  * device (reference: dispatch table, src/gemm/gemm_launcher.cpp:229-247).    */
 int rf_fp8_gemm_choose_split(int m, int n, int k);
 
+/* Allocation-free variant of rf_fp8_gemm.  It has no counterpart in the reference (whose `run`
+ * allocates its scratch lazily with hipMalloc, src/gemm/gemm_launcher.cpp:30-36).
+ *
+ * For callers that cannot allocate device memory where the GEMM runs and cannot pass a scratch
+ * pointer either: code between graph capture and replay, latency-critical threads that must not
+ * enter the CUDA allocator (it can lock and implicitly synchronise the device), and embedders whose
+ * GPU memory belongs to another allocator.  The split-K slices live in a fixed array inside the
+ * loaded library image: RF_STATIC_SCRATCH_BYTES (16 MiB) on every GPU that loads the library, held
+ * until the process exits.  No cudaMalloc/cudaFree or other allocating call is made, at set-up or
+ * per call.
+ *
+ * Limits and rules:
+ *  - split_k * m * n * 4 bytes must fit in RF_STATIC_SCRATCH_BYTES (split_k = 0 lets the library
+ *    choose; the chosen count is subject to the same check).  Otherwise RF_ERR_WORKSPACE is
+ *    returned and a message names the sizes; split_k = 1 never needs scratch.
+ *  - The first call on each device looks up the array's device address and sets kernel attributes;
+ *    make that first call before starting any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's slices.  Nothing in
+ *    it needs clearing (every slice element is rewritten before it is read), but two calls that can
+ *    overlap on the GPU (different streams without an ordering between them) race on it.
+ *  - A bounded device-side wait that expires is recorded in a status word private to this path.  */
+#define RF_STATIC_SCRATCH_BYTES (16u << 20)
+int rf_fp8_gemm_static_scratch(const void *a, const void *b, const float *as, const float *bs, void *c, int m,
+                               int n, int k, int split_k, rf_stream_t stream);
+
 /* Reads and clears the device-side status word of the current device
  * (synchronises the device).  Returns RF_OK or RF_ERR_DEVICE_TIMEOUT; the raw
  * device code is stored in *detail when detail != NULL.

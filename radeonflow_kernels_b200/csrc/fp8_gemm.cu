@@ -430,6 +430,14 @@ extern "C" void rf_debug_wait_stats(unsigned long long* out8, int reset) {
 }
 #endif
 
+cudaError_t fp8_gemm_prepare_device() {
+    cudaError_t e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg128::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Cfg256::kSmemBytes);
+}
+
 cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
                             const CUtensorMap& tma_p, const GemmDestMaps* dests, const GemmParams& p, int block_n,
                             int num_sms, cudaStream_t stream) {

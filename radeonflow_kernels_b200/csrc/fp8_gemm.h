@@ -33,4 +33,12 @@ cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, 
                             const CUtensorMap& tma_p, const GemmDestMaps* dests, const GemmParams& p, int block_n,
                             int num_sms, cudaStream_t stream);
 
+// Sets the launch attributes of every GEMM kernel configuration on the current device (normally done
+// lazily by the first launch of each configuration).
+cudaError_t fp8_gemm_prepare_device();
+
+// The tile width (128 or 256) and K-slice count the library uses for this shape on a device with
+// `num_sms` SMs; `split_k` > 0 forces the slice count.
+void fp8_gemm_plan(int m, int n, int k, int num_sms, int split_k, int* block_n, int* splits);
+
 }  // namespace rf

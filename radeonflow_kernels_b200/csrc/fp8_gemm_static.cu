@@ -1,0 +1,135 @@
+// FP8 block-scaled GEMM for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc on the path where the GEMM runs: code inside a
+// CUDA-graph capture or replay loop, a real-time serving thread that may not take the allocator's
+// locks or trigger an implicit device synchronisation, and embedders whose memory is fully owned by
+// another allocator (an inference server's arena, a framework pool) and who cannot hand this
+// library a scratch pointer through their operator interface.  The ordinary entry points either
+// grow a library-owned buffer with cudaMalloc (`run`) or need a caller buffer (`rf_fp8_gemm`).
+//
+// This variant keeps the split-K slices in a fixed array that is part of the loaded module, so the
+// memory exists as soon as the library is loaded on a GPU and is never allocated or freed at run time.
+// The price is a fixed ceiling and a buffer that every call on the device shares.
+#include "../../include/rf_b200.h"
+#include "fp8_gemm.h"
+#include "host_util.h"
+
+#include <cstdio>
+#include <mutex>
+
+namespace {
+
+// 16 MiB per GPU that loads the library, held until the process exits.
+constexpr size_t kStaticScratchBytes = RF_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+// Device status word of this path (bounded waits record their expiry here); zero when the module loads.
+static __device__ int g_static_status;
+
+struct StaticDevice {
+    bool ready = false;
+    float* scratch = nullptr;   // DEVICE address of g_static_scratch on this device
+    int* status = nullptr;      // DEVICE address of g_static_status on this device
+    int num_sms = 0;
+};
+StaticDevice g_static_dev[rf::kMaxDevices];
+std::mutex g_static_mu;
+
+// Once per device, with that device current.  In host code `g_static_scratch` names a host-side
+// shadow of the symbol, not device memory; the address a kernel may use comes from
+// cudaGetSymbolAddress and differs per device.
+int static_setup(StaticDevice** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= rf::kMaxDevices) return RF_ERR_CUDA;
+    StaticDevice* sd = &g_static_dev[dev];
+    if (!sd->ready) {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        if (!sd->ready) {
+            int major = 0, sms = 0;
+            if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+                return RF_ERR_CUDA;
+            if (major != 10) {
+                fprintf(stderr, "rf_b200: device %d is not sm_100; this library contains sm_100a code only\n", dev);
+                return RF_ERR_UNSUPPORTED;
+            }
+            void* p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+            if (e != cudaSuccess || !p) {
+                fprintf(stderr, "rf_b200: cudaGetSymbolAddress(static scratch) failed: %s\n", cudaGetErrorString(e));
+                return RF_ERR_CUDA;
+            }
+            void* s = nullptr;
+            e = cudaGetSymbolAddress(&s, g_static_status);
+            if (e != cudaSuccess || !s) {
+                fprintf(stderr, "rf_b200: cudaGetSymbolAddress(static status) failed: %s\n", cudaGetErrorString(e));
+                return RF_ERR_CUDA;
+            }
+            if (rf::fp8_gemm_prepare_device() != cudaSuccess) return RF_ERR_CUDA;
+            sd->scratch = static_cast<float*>(p);
+            sd->status = static_cast<int*>(s);
+            sd->num_sms = sms;
+            sd->ready = true;
+        }
+    }
+    *out = sd;
+    return RF_OK;
+}
+
+}  // namespace
+
+extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const float* as, const float* bs, void* c,
+                                          int m, int n, int k, int split_k, rf_stream_t stream) {
+    if (m <= 0 || n <= 0 || k <= 0 || (n % 64) != 0 || (k % 128) != 0) return RF_ERR_BAD_SHAPE;
+    if (!a || !b || !as || !bs || !c) return RF_ERR_NULL_POINTER;
+    if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) return RF_ERR_MISALIGNED;
+    if (((uintptr_t)as | (uintptr_t)bs) & 3) return RF_ERR_MISALIGNED;
+    StaticDevice* sd = nullptr;
+    int rc = static_setup(&sd);
+    if (rc != RF_OK) return rc;
+
+    int bn = 128, splits = 1;
+    rf::fp8_gemm_plan(m, n, k, sd->num_sms, split_k, &bn, &splits);
+    const size_t need = splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
+    if (need > kStaticScratchBytes) {
+        fprintf(stderr,
+                "rf_fp8_gemm_static_scratch: %d K slices of a %d x %d result need %zu bytes of scratch, the built-in "
+                "array holds %zu; pass a smaller split_k (1 needs none) or use rf_fp8_gemm with your own buffer\n",
+                splits, m, n, need, kStaticScratchBytes);
+        return RF_ERR_WORKSPACE;
+    }
+
+    CUtensorMap ta, tb, tc, tp;
+    if (!rf::encode_tma_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)m, (uint64_t)k, (uint64_t)k, 128, 128,
+                           true) ||
+        !rf::encode_tma_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k, (uint64_t)k,
+                           (uint32_t)bn, 128, true) ||
+        !rf::encode_tma_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, (uint64_t)m, (uint64_t)n, (uint64_t)n * 2, 32,
+                           64, true))
+        return RF_ERR_CUDA;
+    if (splits > 1) {
+        if (!rf::encode_tma_3d(&tp, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, sd->scratch, (uint64_t)n, (uint64_t)m,
+                               (uint64_t)splits, 32, 32, true))
+            return RF_ERR_CUDA;
+    } else {
+        tp = tc;
+    }
+    rf::GemmParams p;
+    p.a_scale = as;
+    p.b_scale = bs;
+    p.c = static_cast<__nv_bfloat16*>(c);
+    p.partial = splits > 1 ? sd->scratch : nullptr;   // every element of the slices is overwritten: nothing to clear
+    p.status = sd->status;
+    p.m = m; p.n = n; p.k = k;
+    p.tiles_m = (m + 127) / 128;
+    p.tiles_n = (n + bn - 1) / bn;
+    p.splits = splits;
+    p.n_dest = 1;
+    p.c_col_offset = 0;
+    cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, nullptr, p, bn, sd->num_sms,
+                                        reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        fprintf(stderr, "rf_fp8_gemm_static_scratch: launch failed: %s\n", cudaGetErrorString(e));
+        return RF_ERR_CUDA;
+    }
+    return RF_OK;
+}

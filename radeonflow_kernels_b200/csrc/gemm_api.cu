@@ -155,6 +155,16 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
 
 }  // namespace
 
+namespace rf {
+void fp8_gemm_plan(int m, int n, int k, int num_sms, int split_k, int* block_n, int* splits) {
+    const int kb = k / kBlockK;
+    if (split_k > kb) split_k = kb;
+    const GemmPlan plan = choose_plan(m, n, k, num_sms, split_k);
+    *block_n = plan.block_n;
+    *splits = plan.splits;
+}
+}  // namespace rf
+
 extern "C" {
 
 const char* rf_version(void) { return "rf_b200 0.1 sm_100a"; }
