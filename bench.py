@@ -309,8 +309,9 @@ def run_extras(args, rank, world, dev, dist, peaks):
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
     fl = moe_layer_flops(t_total, d, f, e, k)
     out["moe_expert_parallel"] = {
-        "config": "32768 tokens, d=7168 f=2048 E=256 top-8 + 1 shared, Zipf(1.1) router bias, experts sharded "
-                  "E/N per GPU, dispatch by peer stores, combine by peer loads",
+        "config": "32768 tokens, d=7168 f=2048 E=256 top-8 + 1 shared, Zipf(1.1) router bias; experts sharded E/N "
+                  "per GPU by a static load-aware placement from one calibration pass; dispatch by peer stores, "
+                  "combine by peer loads",
         "ms_per_layer": ms, "tokens_per_s": t_total / (ms * 1e-3), "tflops_total": fl / (ms * 1e-3) / 1e12,
         "scaling": "strong", "rows_per_gpu_max": mx.item(), "rows_per_gpu_mean": sm.item() / world,
         "imbalance_max_over_mean": mx.item() / (sm.item() / world)}

@@ -47,20 +47,26 @@ constexpr int BK = 128;          // one scale block, one 128-byte swizzle row of
 constexpr int UMMA_K = 32;       // K per tcgen05.mma for 8-bit operands
 constexpr int NUM_NON_EPI_WARPS = 4;
 
-template <int BN, int STAGES>
+// TWO_CTA: the tile is 256 x BN per CTA PAIR (2-CTA cluster): each CTA loads its own 128 rows of A and
+// half of the B rows, the leader CTA issues cta_group::2 MMAs (M = 256) whose accumulator rows
+// 0-127 / 128-255 land in the two CTAs' TMEM.  Per SM and K block this moves 32 KB through shared
+// memory each way instead of 48 KB, which is what bounds the 1-CTA tile.
+template <int BN, int STAGES, bool TWO_CTA = false>
 struct GemmCfg {
     static constexpr int kBN = BN;
     static constexpr int kStages = STAGES;
+    static constexpr bool kTwoCta = TWO_CTA;
+    static constexpr int kBRows = TWO_CTA ? BN / 2 : BN;       // rows of B this CTA loads per K block
     static constexpr int kEpiGroups = 2;                       // column groups, 4 warps each
     static constexpr int kColsPerThread = BN / kEpiGroups;     // 64 or 128: one scale block at most
     static constexpr int kEpiWarps = 4 * kEpiGroups;
     static constexpr int kThreads = 32 * (NUM_NON_EPI_WARPS + kEpiWarps);   // 384
     static constexpr int kABytes = BM * BK;
-    static constexpr int kBBytes = BN * BK;
+    static constexpr int kBBytes = kBRows * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemBufs = 512 / BN;                // accumulator buffers in flight
     static constexpr int kTmemCols = kTmemBufs * BN;          // all 512 TMEM columns
-    static constexpr int kBarBytes = (2 * STAGES + 2 * kTmemBufs) * 8 + 16;
+    static constexpr int kBarBytes = (3 * STAGES + 2 * kTmemBufs) * 8 + 16;
     static constexpr int kSlabBytes = 32 * 128;               // per epilogue warp: 32 rows x 128 B, swizzled
     static constexpr int kSmemBytes =
         STAGES * kStageBytes + kEpiWarps * kSlabBytes + kBarBytes + 1024;       // + alignment slack
@@ -113,12 +119,17 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
     auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + NBUF + b); };
-    const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 2 * NBUF);
+    auto peer_full_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 * NBUF + s); };   // leader only
+    const uint32_t tmem_slot = bar_base + 8u * (3 * STAGES + 2 * NBUF);
     uint32_t* tmem_slot_ptr =
         reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    constexpr bool TWO = Cfg::kTwoCta;
+    const uint32_t cta_rank = TWO ? cluster_ctarank() : 0u;      // 0 = leader of the pair
+    const int unit = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;          // work-loop index
+    const int unit_stride = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tma_a);
@@ -128,18 +139,26 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
+        for (int s = 0; s < STAGES; ++s) mbar_init(peer_full_bar(s), 1);
         for (int b = 0; b < NBUF; ++b) {
             mbar_init(tmem_full_bar(b), 1);
-            mbar_init(tmem_empty_bar(b), Cfg::kEpiWarps);
+            // in a CTA pair the leader's barrier collects the epilogue warps of both CTAs
+            mbar_init(tmem_empty_bar(b), TWO ? 2 * Cfg::kEpiWarps : Cfg::kEpiWarps);
         }
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, Cfg::kTmemCols);
-        tmem_relinquish();
+        if (TWO) {
+            tmem_alloc_2cta(tmem_slot, Cfg::kTmemCols);
+            tmem_relinquish_2cta();
+        } else {
+            tmem_alloc(tmem_slot, Cfg::kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (TWO) cluster_sync_all();     // both CTAs' barriers exist before any remote arrive or multicast commit
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot_ptr);
 
@@ -147,7 +166,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const int kb_total = p.k / BK;
 
     if (warp < NUM_NON_EPI_WARPS) {
-    if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+    if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 120;\n");
     // Producer and MMA warps keep all 32 lanes in the loops (warp-uniform control
     // flow, so descriptors and addresses live in uniform registers) and elect one
     // lane only for the instructions that must be issued once.
@@ -156,10 +175,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         uint32_t it = 0;  // running K-block counter across work items
         bool ok = true;
         long long w_empty = 0; (void)w_empty;
-        for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        for (int w = unit; w < total_work && ok; w += unit_stride) {
             const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
             const int kb0 = (int)((long long)kb_total * t.split / p.splits);
             const int kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
+            // rows of A and of B this CTA fetches (a CTA pair splits both between its two CTAs)
+            const int a_row0 = TWO ? (t.m_blk * 2 + (int)cta_rank) * BM : t.m_blk * BM;
+            const int b_row0 = t.n_blk * BN + (TWO ? (int)cta_rank * Cfg::kBRows : 0);
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
@@ -170,8 +192,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 if (elect_one()) {
                     mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
                     const uint32_t sa = smem_base + s * Cfg::kStageBytes;
-                    tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, t.m_blk * BM);
-                    tma_load_2d(sa + Cfg::kABytes, &tma_b, full_bar(s), kb * BK, t.n_blk * BN);
+                    tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, a_row0);
+                    tma_load_2d(sa + Cfg::kABytes, &tma_b, full_bar(s), kb * BK, b_row0);
                 }
                 __syncwarp();
             }
@@ -179,11 +201,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         if (lane == 0) { RF_STAT_FLUSH(0, w_empty); }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
-        constexpr uint32_t idesc = make_idesc(BM, BN, /*e4m3*/ 0, /*e4m3*/ 0, 0, 0);
+        constexpr uint32_t idesc = make_idesc(TWO ? 2 * BM : BM, BN, /*e4m3*/ 0, /*e4m3*/ 0, 0, 0);
         uint32_t it = 0;
         bool ok = true;
         long long w_tmem = 0, w_full = 0; (void)w_tmem; (void)w_full;
-        for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        for (int w = unit; w < total_work && ok; w += unit_stride) {
             const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
             const int kb0 = (int)((long long)kb_total * t.split / p.splits);
             const int kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
@@ -192,6 +214,17 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 const uint32_t ph = (it / STAGES) & 1;
                 const int buf = it % NBUF;
                 const uint32_t bph = (it / NBUF) & 1;
+                if (TWO && cta_rank != 0) {
+                    // Second CTA of the pair: it issues no MMA.  This warp relays "my stage has landed"
+                    // to the leader (a TMA load can only signal a barrier of the CTA it writes to).
+                    ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, kErrMmaWaitFull));
+                    if (!ok) break;
+                    // (no memory ordering needed: the stage was written by the TMA and is read by the
+                    // tensor core, both through the async proxy; the barrier flip means the bytes landed)
+                    if (elect_one()) mbar_arrive_cluster_relaxed(mapa_cluster(peer_full_bar(s), 0));
+                    __syncwarp();
+                    continue;
+                }
                 { RF_STAT_BEGIN();
                 ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(buf), bph ^ 1, p.status, kErrMmaWaitTmem));
                 RF_STAT_END(w_tmem); }
@@ -200,6 +233,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, kErrMmaWaitFull));
                 RF_STAT_END(w_full); }
                 if (!ok) break;
+                if (TWO) {
+                    RF_STAT_BEGIN();
+                    ok = __all_sync(0xffffffffu, mbar_wait(peer_full_bar(s), ph, p.status, kErrMmaWaitFull));
+                    RF_STAT_END(w_full);
+                    if (!ok) break;
+                }
                 tc_fence_after();
                 const uint32_t sa = smem_base + s * Cfg::kStageBytes;
                 const uint64_t adesc = smem_desc_kmajor_sw128(sa);
@@ -209,12 +248,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
                         // +32 bytes along K inside the swizzled row = +2 in the (addr >> 4) field
-                        umma_f8(d, adesc + 2 * j, bdesc + 2 * j, idesc, j > 0 ? 1u : 0u);
+                        if (TWO) umma_f8_2cta(d, adesc + 2 * j, bdesc + 2 * j, idesc, j > 0 ? 1u : 0u);
+                        else umma_f8(d, adesc + 2 * j, bdesc + 2 * j, idesc, j > 0 ? 1u : 0u);
                     }
                     // One commit per K block (every tcgen05 instruction costs tensor-pipe
                     // issue time): it publishes the accumulator buffer, and the epilogue,
                     // which observes it, releases the smem stage on the MMA warp's behalf.
-                    umma_commit(tmem_full_bar(buf));
+                    if (TWO) umma_commit_2cta_multicast(tmem_full_bar(buf), 0x3);   // same barrier in both CTAs
+                    else umma_commit(tmem_full_bar(buf));
                 }
                 __syncwarp();
             }
@@ -223,7 +264,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
     } else {
         // ---------------------------------------------------------- epilogue
-        if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;\n");
+        if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 192;\n");
         const int ew = warp - NUM_NON_EPI_WARPS;
         const int quad = warp & 3;            // TMEM lane quadrant this warp may access
         const int grp = ew >> 2;              // column group
@@ -236,11 +277,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #ifdef RF_WAIT_STATS
         const long long t_begin = clock64();
 #endif
-        for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        // (in a CTA pair tmem_empty lives in the leader CTA, the only MMA issuer; both CTAs arrive on it
+        // through the cluster window)
+        for (int w = unit; w < total_work && ok; w += unit_stride) {
             const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
             const int kb0 = (int)((long long)kb_total * t.split / p.splits);
             const int kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
-            const int row = t.m_blk * BM + row_in_tile;
+            const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
+            const int row = cta_m_blk * BM + row_in_tile;
             const int col0 = t.n_blk * BN + grp * CPT;
             const bool row_ok = row < p.m;
             const int nb = col0 >> 7;
@@ -283,22 +327,30 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 if (ew == 0 && lane == 0) mbar_arrive(empty_bar(it % STAGES));
                 const uint32_t taddr = lane_addr + buf * BN + grp * CPT;
                 constexpr int NCH = CPT / 32;
-                float v[2][32];
+                // Staging registers: two 32-column buffers (the load of chunk c+1 overlaps the FMAs of
+                // chunk c) when a thread owns 64 columns; one buffer when it owns 128, because 128
+                // accumulators leave no room for a second one (the other epilogue warp on the same
+                // scheduler covers the load latency instead).
+                constexpr int NV = CPT > 64 ? 1 : 2;
+                float v[NV][32];
                 tmem_ld32_async(taddr, v[0]);
 #pragma unroll
                 for (int c = 0; c < NCH; ++c) {
-                    tmem_ld_fence(v[c & 1]);   // waits for every load issued so far
-                    if (c + 1 < NCH) {
-                        tmem_ld32_async(taddr + (c + 1) * 32, v[(c + 1) & 1]);   // overlaps the FMAs below
-                    } else {
+                    tmem_ld_fence(v[c % NV]);   // waits for every load issued so far
+                    if (NV == 2 && c + 1 < NCH) tmem_ld32_async(taddr + (c + 1) * 32, v[(c + 1) % NV]);
+                    if (c + 1 == NCH) {
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+                        if (lane == 0) {
+                            if (TWO) mbar_arrive_cluster_relaxed(mapa_cluster(tmem_empty_bar(buf), 0));
+                            else mbar_arrive(tmem_empty_bar(buf));
+                        }
                     }
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         acc[c * 16 + j] =
-                            __ffma2_rn(make_float2(v[c & 1][2 * j], v[c & 1][2 * j + 1]), s2, acc[c * 16 + j]);
+                            __ffma2_rn(make_float2(v[c % NV][2 * j], v[c % NV][2 * j + 1]), s2, acc[c * 16 + j]);
+                    if (NV == 1 && c + 1 < NCH) tmem_ld32_async(taddr + (c + 1) * 32, v[0]);
                 }
             }
             if (!ok) break;
@@ -309,7 +361,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             {
                 const uint32_t slab = slab_base + ew * Cfg::kSlabBytes;
                 const uint32_t my_row = slab + lane * 128;
-                const int slab_row0 = t.m_blk * BM + quad * 32;
+                const int slab_row0 = cta_m_blk * BM + quad * 32;
                 if (p.splits == 1) {
 #pragma unroll
                     for (int ch = 0; ch < CPT / 64; ++ch) {
@@ -372,9 +424,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     // ------------------------------------------------------------- tear-down
     tc_fence_before();
     __syncthreads();
+    if (TWO) cluster_sync_all();     // the peer no longer touches this CTA's barriers, smem or TMEM
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+        if (TWO) tmem_dealloc_2cta(tmem_base, Cfg::kTmemCols);
+        else tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
 }
 
@@ -397,6 +451,7 @@ splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restric
 
 using Cfg128 = GemmCfg<128, 6>;
 using Cfg256 = GemmCfg<256, 4>;
+using CfgPair = GemmCfg<256, 6, true>;      // 256 x 256 tile per CTA pair
 
 template <class Cfg>
 cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
@@ -412,9 +467,26 @@ cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const
         attr_set[dev] = true;
     }
     const int total = p.tiles_m * p.tiles_n * p.splits;
-    const int grid = total < num_sms ? total : num_sms;
-    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tma_a, tma_b, tma_c, tma_p, dests, p);
-    return cudaGetLastError();
+    if (!Cfg::kTwoCta) {
+        const int grid = total < num_sms ? total : num_sms;
+        kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tma_a, tma_b, tma_c, tma_p, dests, p);
+        return cudaGetLastError();
+    }
+    // CTA pairs: clusters of 2 along x, one pair per work item at most
+    const int pairs = total < num_sms / 2 ? total : num_sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, tma_a, tma_b, tma_c, tma_p, dests, p);
 }
 
 }  // namespace
@@ -434,8 +506,11 @@ cudaError_t fp8_gemm_prepare_device() {
     cudaError_t e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg128::kSmemBytes);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                Cfg256::kSmemBytes);
+    e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg256::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(fp8_gemm_kernel<CfgPair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                CfgPair::kSmemBytes);
 }
 
 cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
@@ -446,8 +521,10 @@ cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, 
         for (int i = 0; i < 8; ++i) local.m[i] = tma_c;
         dests = &local;
     }
-    cudaError_t e = block_n == 256 ? launch_cfg<Cfg256>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
-                                   : launch_cfg<Cfg128>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream);
+    // block_n: 128 / 256 = one-CTA tiles of that width; 512 = the CTA-pair configuration (256 x 256 per pair)
+    cudaError_t e = block_n == 512   ? launch_cfg<CfgPair>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
+                    : block_n == 256 ? launch_cfg<Cfg256>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
+                                     : launch_cfg<Cfg128>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream);
     if (e != cudaSuccess) return e;
     if (p.splits > 1) {
         const size_t mn = (size_t)p.m * p.n;

@@ -24,8 +24,14 @@ struct GemmDestMaps {
     CUtensorMap m[8];
 };
 
+// Tile configurations, named by `block_n`: 128 and 256 are one-CTA tiles 128 x block_n; 512 is the
+// CTA-pair configuration (256 x 256 per 2-CTA cluster, each CTA loading 128 rows of A and of B).
+inline int gemm_tile_rows(int block_n) { return block_n == 512 ? 256 : 128; }
+inline int gemm_tile_cols(int block_n) { return block_n == 512 ? 256 : block_n; }
+inline int gemm_b_box_rows(int block_n) { return block_n == 512 ? 128 : block_n; }
+
 // Launches the GEMM (and the split-K fix-up when p.splits > 1) on `stream`.
-// `block_n` is the tile width the tensor map of B and p.tiles_n were built for: 128 or 256.
+// `block_n` is the configuration the tensor map of B and p.tiles_m / p.tiles_n were built for.
 // `tma_c` stores bf16 C boxes of 32 rows x 64 columns; `tma_p` (used when p.splits > 1) stores fp32
 // slice boxes of 32 rows x 32 columns into the [splits][m][n] scratch.
 // When p.n_dest > 1, `dests` holds p.n_dest maps and replaces tma_c (split-K is not combined with it).

@@ -102,7 +102,7 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
     if (!rf::encode_tma_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)m, (uint64_t)k, (uint64_t)k, 128, 128,
                            true) ||
         !rf::encode_tma_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k, (uint64_t)k,
-                           (uint32_t)bn, 128, true) ||
+                           (uint32_t)rf::gemm_b_box_rows(bn), 128, true) ||
         !rf::encode_tma_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, (uint64_t)m, (uint64_t)n, (uint64_t)n * 2, 32,
                            64, true))
         return RF_ERR_CUDA;
@@ -120,8 +120,8 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
     p.partial = splits > 1 ? sd->scratch : nullptr;   // every element of the slices is overwritten: nothing to clear
     p.status = sd->status;
     p.m = m; p.n = n; p.k = k;
-    p.tiles_m = (m + 127) / 128;
-    p.tiles_n = (n + bn - 1) / bn;
+    p.tiles_m = (m + rf::gemm_tile_rows(bn) - 1) / rf::gemm_tile_rows(bn);
+    p.tiles_n = (n + rf::gemm_tile_cols(bn) - 1) / rf::gemm_tile_cols(bn);
     p.splits = splits;
     p.n_dest = 1;
     p.c_col_offset = 0;

@@ -13,15 +13,28 @@ constexpr int kBlockK = 128;
 
 bool shape_ok(int m, int n, int k) { return m > 0 && n > 0 && k > 0 && (n % 64) == 0 && (k % kBlockK) == 0; }
 
-// Tuning knob for experiments: RF_FP8_GEMM_BN=128|256 forces the tile width.
+// Tuning knob for experiments: RF_FP8_GEMM_BN=128|256|512 forces the tile configuration (512 = CTA pair).
 int forced_block_n() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("RF_FP8_GEMM_BN");
         v = e ? atoi(e) : 0;
-        if (v != 128 && v != 256) v = 0;
+        if (v != 128 && v != 256 && v != 512) v = 0;
     }
     return v;
+}
+
+// The CTA-pair configuration (cta_group::2, 256 x 256 per 2-CTA cluster) is correct and selectable
+// (RF_FP8_GEMM_BN=512, or RF_FP8_GEMM_PAIR=1 to let the planner consider it) but is not chosen by
+// default: measured on B200 it runs 6144x4608x7168 at 2.05 PFLOP/s against 2.2 for the one-CTA 128 x 256
+// tile, because the per-K-block accumulator hand-off, not shared-memory bandwidth, bounds both.
+bool pair_config_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RF_FP8_GEMM_PAIR");
+        v = (e && atoi(e) == 1) ? 1 : 0;
+    }
+    return v == 1;
 }
 
 struct GemmPlan {
@@ -34,9 +47,12 @@ struct GemmPlan {
 // (about 0.14 us): rounds of tiles over the SMs x (K blocks per slice + fixed per-tile cost),
 // plus, for split-K, the fp32 slice round trip through HBM and the second launch.
 GemmPlan plan_for(int m, int n, int k, int num_sms, int bn, int forced_split) {
-    const int tiles = ((m + 127) / 128) * ((n + bn - 1) / bn);
+    const int tr = rf::gemm_tile_rows(bn), tc = rf::gemm_tile_cols(bn);
+    const int tiles = ((m + tr - 1) / tr) * ((n + tc - 1) / tc);
     const int kb = k / kBlockK;
-    const double tile_w = bn / 128.0;
+    if (bn == 512) num_sms /= 2;     // work items go to CTA pairs
+    // measured cycles per K block of one work item / 256: 128x128 ~ 660, 128x256 ~ 790, pair 256x256 ~ 700
+    const double tile_w = bn == 512 ? 2.7 : (bn == 256 ? 3.1 : 2.6);
     GemmPlan best{bn, 1, 1e30};
     for (int s = 1; s <= 8; ++s) {
         if (forced_split > 0 && s != forced_split) continue;
@@ -44,7 +60,7 @@ GemmPlan plan_for(int m, int n, int k, int num_sms, int bn, int forced_split) {
         if (s > kb) break;
         const int rounds = (tiles * s + num_sms - 1) / num_sms;
         const int kb_per = (kb + s - 1) / s;
-        double cost = (double)rounds * (kb_per * tile_w + 4.0);
+        double cost = (double)rounds * (kb_per * tile_w + 8.0);
         if (s > 1) {
             const double bytes = 8.0 * s * (double)m * n + 2.0 * (double)m * n;
             cost += (bytes / 6.0e12 + 2.5e-6) / 0.14e-6;
@@ -62,7 +78,12 @@ GemmPlan choose_plan(int m, int n, int k, int num_sms, int forced_split) {
     GemmPlan p256 = plan_for(m, n, k, num_sms, 256, forced_split);
     // Wide tiles halve the A traffic and the MMA instruction count per FLOP; prefer them unless
     // they cost noticeably more rounds (ragged N such as 576, or too few tiles).
-    return p256.cost <= p128.cost * 1.02 ? p256 : p128;
+    GemmPlan best = p256.cost <= p128.cost * 1.02 ? p256 : p128;
+    if (pair_config_enabled()) {
+        GemmPlan pp = plan_for(m, n, k, num_sms, 512, forced_split);
+        if (pp.cost < best.cost) best = pp;
+    }
+    return best;
 }
 
 // `dest_c` / `n_dest` / `dest_n` / `col_offset`: when n_dest > 1 the [m, n] result is written at column
@@ -109,7 +130,7 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
                            true))
         return RF_ERR_CUDA;
     if (!rf::encode_tma_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k, (uint64_t)k,
-                           (uint32_t)bn, 128, true))
+                           (uint32_t)rf::gemm_b_box_rows(bn), 128, true))
         return RF_ERR_CUDA;
 
     CUtensorMap tc, tp;
@@ -131,8 +152,8 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     p.partial = partial;
     p.status = st->status;
     p.m = m; p.n = n; p.k = k;
-    p.tiles_m = (m + 127) / 128;
-    p.tiles_n = (n + bn - 1) / bn;
+    p.tiles_m = (m + rf::gemm_tile_rows(bn) - 1) / rf::gemm_tile_rows(bn);
+    p.tiles_n = (n + rf::gemm_tile_cols(bn) - 1) / rf::gemm_tile_cols(bn);
     p.splits = splits;
     p.n_dest = n_dest;
     p.c_col_offset = col_offset;

@@ -12,6 +12,16 @@ namespace rf {
 
 namespace {
 
+// Select one of the (at most 8) peer pointers without indexing the kernel-parameter struct
+// dynamically (which would force a copy of the struct into local memory).
+__device__ __forceinline__ void* pick_peer(const PeerPtrs& pp, int q) {
+    void* r = pp.p[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+        if (q == i) r = pp.p[i];
+    return r;
+}
+
 __global__ void __launch_bounds__(1024)
 ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_experts, int* __restrict__ send_base,
                  int* __restrict__ recv_offsets) {
@@ -54,7 +64,7 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted
         const int q = e / experts_per_rank;
         const int row = send_base[e] + (p - first_token_offset[e]);
         const int tok = permuted_rows[p] % n_tokens;
-        uint4* dst = static_cast<uint4*>(recv_x.p[q]) + (size_t)row * vec_per_row + v;
+        uint4* dst = static_cast<uint4*>(pick_peer(recv_x, q)) + (size_t)row * vec_per_row + v;
         *dst = __ldg(x + (size_t)tok * vec_per_row + v);
         if (v == 0) {
             pair_rank[p] = q;
@@ -72,7 +82,7 @@ ep_combine_kernel(PeerPtrs y, const uint4* __restrict__ shared_out, const int* _
     __shared__ float w_s[8];
     if (threadIdx.x < top_k) {
         const int p = rev[threadIdx.x * n_tokens + t];
-        src_s[threadIdx.x] = static_cast<const uint4*>(y.p[pair_rank[p]]) + (size_t)pair_row[p] * vec_per_row;
+        src_s[threadIdx.x] = static_cast<const uint4*>(pick_peer(y, pair_rank[p])) + (size_t)pair_row[p] * vec_per_row;
         w_s[threadIdx.x] = __half2float(weights[p]);
     }
     __syncthreads();
@@ -80,8 +90,16 @@ ep_combine_kernel(PeerPtrs y, const uint4* __restrict__ shared_out, const int* _
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int i = 0; i < top_k; ++i) {
-            const uint4 q = src_s[i][v];            // peer (or local) load
+        // all k row segments are requested before the first is used: k independent loads in flight
+        // per thread (the rows sit in other GPUs' memory, a round trip of microseconds)
+        uint4 qv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (i < top_k) qv[i] = src_s[i][v];     // peer (or local) load
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i >= top_k) continue;
+            const uint4 q = qv[i];
             const __half2* h = reinterpret_cast<const __half2*>(&q);
             const float w = w_s[i];
 #pragma unroll

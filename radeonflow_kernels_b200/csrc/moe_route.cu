@@ -256,8 +256,15 @@ combine_kernel(const uint4* __restrict__ y, const uint4* __restrict__ shared_out
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int i = 0; i < top_k; ++i) {
-            const uint4 q = __ldg(y + (size_t)pos_s[i] * vec_per_row + v);
+        // all k row segments are requested before the first is used
+        uint4 qv[MAX_K];
+#pragma unroll
+        for (int i = 0; i < MAX_K; ++i)
+            if (i < top_k) qv[i] = __ldg(y + (size_t)pos_s[i] * vec_per_row + v);
+#pragma unroll
+        for (int i = 0; i < MAX_K; ++i) {
+            if (i >= top_k) continue;
+            const uint4 q = qv[i];
             const __half2* h = reinterpret_cast<const __half2*>(&q);
             const float w = w_s[i];
 #pragma unroll

@@ -156,3 +156,30 @@ def test_perf_metrics_are_filled(rf_lib):
     rf_lib.run(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(), c.data_ptr(), 1024, 1536, 7168,
                ctypes.byref(pm), None)
     assert pm.count >= 1 and pm.entries[0].time > 0 and pm.entries[0].gflops > 0
+
+
+def test_cta_pair_configuration_matches_oracle():
+    """The cta_group::2 configuration (256 x 256 tile per 2-CTA cluster) is selected per process by an
+    environment variable, so it runs in a child process."""
+    import subprocess
+    import sys
+    code = r'''
+import os, sys
+import numpy as np, torch
+sys.path.insert(0, os.environ["RF_ROOT"])
+from oracle import fp8_gemm as o
+from radeonflow_kernels_b200 import gemm as G
+for (m, n, k, split, dist) in [(300, 576, 1024, 1, "randn"), (1024, 1536, 7168, 1, "randn"), (512, 512, 2048, 2, "baseline")]:
+    a, b, a_s, b_s = o.generate_input(m, n, k, 5, dist)
+    d = lambda x, t=None: (torch.from_numpy(x).cuda().view(t) if t else torch.from_numpy(x).cuda())
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.fp8_mm(d(a, torch.float8_e4m3fn), d(b, torch.float8_e4m3fn), d(a_s), d(b_s), c, split_k=split)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    ok, nbad, mx = o.check(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a, b, a_s, b_s))
+    assert ok, (m, n, k, nbad, mx)
+print("PAIR OK")
+'''
+    env = dict(os.environ, RF_FP8_GEMM_BN="512", RF_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "PAIR OK" in res.stdout, (res.stdout + res.stderr)[-3000:]
