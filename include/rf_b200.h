@@ -80,6 +80,15 @@ size_t rf_fp8_gemm_workspace_bytes(int m, int n, int k, int split_k);
  * device (reference: dispatch table, src/gemm/gemm_launcher.cpp:229-247).    */
 int rf_fp8_gemm_choose_split(int m, int n, int k);
 
+/* Same arithmetic with the operands in the reference's own physical layout
+ * (src/gemm/gemm_kernel_legacy.cpp:264-268; scripts/problems/gemm/reference.py:28-37 creates (k,m) and
+ * returns .T): a [k][m], b [k][n] (m / n contiguous), as [k/128][m], bs [k/128][ceil(n/128)], c [m][n].
+ * The tiles are consumed as MN-major tensor-core operands, so the reference's two transpose passes
+ * (src/gemm/gemm_launcher.cpp:55-56, src/gemm/transpose_kernel.cpp) have no counterpart.  m % 16 == 0.
+ * Bytes are still OCP e4m3fn.  workspace == NULL uses the library-owned scratch.               */
+int rf_fp8_gemm_colmajor(const void *a, const void *b, const float *as, const float *bs, void *c, int m, int n,
+                         int k, void *workspace, size_t workspace_bytes, rf_stream_t stream);
+
 /* Allocation-free variant of rf_fp8_gemm.  It has no counterpart in the reference (whose `run`
  * allocates its scratch lazily with hipMalloc, src/gemm/gemm_launcher.cpp:30-36).
  *

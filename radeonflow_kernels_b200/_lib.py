@@ -90,6 +90,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_fp8_gemm_workspace_bytes.argtypes = [ci, ci, ci, ci]
     L.rf_fp8_gemm_choose_split.restype = ci
     L.rf_fp8_gemm_choose_split.argtypes = [ci, ci, ci]
+    L.rf_fp8_gemm_colmajor.restype = ci
+    L.rf_fp8_gemm_colmajor.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp, sz, vp]
     L.rf_fp8_gemm_static_scratch.restype = ci
     L.rf_fp8_gemm_static_scratch.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
     # ---- MoE

@@ -51,11 +51,16 @@ constexpr int NUM_NON_EPI_WARPS = 4;
 // half of the B rows, the leader CTA issues cta_group::2 MMAs (M = 256) whose accumulator rows
 // 0-127 / 128-255 land in the two CTAs' TMEM.  Per SM and K block this moves 32 KB through shared
 // memory each way instead of 48 KB, which is what bounds the 1-CTA tile.
-template <int BN, int STAGES, bool TWO_CTA = false>
+// MN_MAJOR: operands stored [k][m] and [k][n] (M / N contiguous), the reference's physical layout
+// (src/gemm/gemm_kernel_legacy.cpp:264-268); consumed directly as MN-major UMMA operands, so the
+// reference's transpose pass (src/gemm/gemm_launcher.cpp:55-56) has no counterpart here.
+template <int BN, int STAGES, bool TWO_CTA = false, bool MN_MAJOR = false>
 struct GemmCfg {
     static constexpr int kBN = BN;
     static constexpr int kStages = STAGES;
     static constexpr bool kTwoCta = TWO_CTA;
+    static constexpr bool kMnMajor = MN_MAJOR;
+    static_assert(!(TWO_CTA && MN_MAJOR), "the CTA-pair configuration is K-major only");
     static constexpr int kBRows = TWO_CTA ? BN / 2 : BN;       // rows of B this CTA loads per K block
     static constexpr int kEpiGroups = 2;                       // column groups, 4 warps each
     static constexpr int kColsPerThread = BN / kEpiGroups;     // 64 or 128: one scale block at most
@@ -192,8 +197,17 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 if (elect_one()) {
                     mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
                     const uint32_t sa = smem_base + s * Cfg::kStageBytes;
-                    tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, a_row0);
-                    tma_load_2d(sa + Cfg::kABytes, &tma_b, full_bar(s), kb * BK, b_row0);
+                    if (Cfg::kMnMajor) {
+                        // boxes of 128 K-rows x 128 bytes of M (or N); B needs one box per 128 columns
+                        tma_load_2d(sa, &tma_a, full_bar(s), a_row0, kb * BK);
+#pragma unroll
+                        for (int j = 0; j < BN / 128; ++j)
+                            tma_load_2d(sa + Cfg::kABytes + j * (BK * 128), &tma_b, full_bar(s), b_row0 + 128 * j,
+                                        kb * BK);
+                    } else {
+                        tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, a_row0);
+                        tma_load_2d(sa + Cfg::kABytes, &tma_b, full_bar(s), kb * BK, b_row0);
+                    }
                 }
                 __syncwarp();
             }
@@ -201,7 +215,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         if (lane == 0) { RF_STAT_FLUSH(0, w_empty); }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
-        constexpr uint32_t idesc = make_idesc(TWO ? 2 * BM : BM, BN, /*e4m3*/ 0, /*e4m3*/ 0, 0, 0);
+        constexpr uint32_t idesc = make_idesc(TWO ? 2 * BM : BM, BN, /*e4m3*/ 0, /*e4m3*/ 0,
+                                              Cfg::kMnMajor ? 1 : 0, Cfg::kMnMajor ? 1 : 0);
+        // descriptor advance per MMA (K = 32): 32 bytes inside the swizzled row for K-major operands,
+        // 32 K-rows of 128 bytes for MN-major ones (address field is in 16-byte units)
+        constexpr uint32_t kstep = Cfg::kMnMajor ? (UMMA_K * 128) / 16 : UMMA_K / 16;
         uint32_t it = 0;
         bool ok = true;
         long long w_tmem = 0, w_full = 0; (void)w_tmem; (void)w_full;
@@ -241,15 +259,16 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 }
                 tc_fence_after();
                 const uint32_t sa = smem_base + s * Cfg::kStageBytes;
-                const uint64_t adesc = smem_desc_kmajor_sw128(sa);
-                const uint64_t bdesc = smem_desc_kmajor_sw128(sa + Cfg::kABytes);
+                const uint64_t adesc = Cfg::kMnMajor ? smem_desc_mnmajor_sw128(sa, BK * 128, 1024)
+                                                     : smem_desc_kmajor_sw128(sa);
+                const uint64_t bdesc = Cfg::kMnMajor ? smem_desc_mnmajor_sw128(sa + Cfg::kABytes, BK * 128, 1024)
+                                                     : smem_desc_kmajor_sw128(sa + Cfg::kABytes);
                 const uint32_t d = tmem_base + buf * BN;
                 if (elect_one()) {
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
-                        // +32 bytes along K inside the swizzled row = +2 in the (addr >> 4) field
-                        if (TWO) umma_f8_2cta(d, adesc + 2 * j, bdesc + 2 * j, idesc, j > 0 ? 1u : 0u);
-                        else umma_f8(d, adesc + 2 * j, bdesc + 2 * j, idesc, j > 0 ? 1u : 0u);
+                        if (TWO) umma_f8_2cta(d, adesc + kstep * j, bdesc + kstep * j, idesc, j > 0 ? 1u : 0u);
+                        else umma_f8(d, adesc + kstep * j, bdesc + kstep * j, idesc, j > 0 ? 1u : 0u);
                     }
                     // One commit per K block (every tcgen05 instruction costs tensor-pipe
                     // issue time): it publishes the accumulator buffer, and the epilogue,
@@ -270,7 +289,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         const int grp = ew >> 2;              // column group
         const int row_in_tile = quad * 32 + lane;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-        const int kbs = p.k / BK;
         uint32_t it = 0;
         bool ok = true;
         long long w_acc = 0, w_total = 0; (void)w_acc; (void)w_total;
@@ -289,8 +307,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const bool row_ok = row < p.m;
             const int nb = col0 >> 7;
             const bool nb_ok = col0 < p.n;
-            const float* as_row = p.a_scale + (size_t)(row_ok ? row : 0) * kbs;
-            const float* bs_row = p.b_scale + (size_t)(nb_ok ? nb : 0) * kbs;
+            const float* as_row = p.a_scale + (size_t)(row_ok ? row : 0) * p.as_row_stride;
+            const float* bs_row = p.b_scale + (size_t)(nb_ok ? nb : 0) * p.bs_row_stride;
+            const long long as_ks = p.as_k_stride, bs_ks = p.bs_k_stride;
 
             float2 acc[CPT / 2];
 #pragma unroll
@@ -303,8 +322,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #pragma unroll
             for (int d = 0; d < PF; ++d) {
                 const int kk = min(kb0 + d, kb1 - 1);
-                qa[d] = __ldg(as_row + kk);
-                qb[d] = __ldg(bs_row + kk);
+                qa[d] = __ldg(as_row + kk * as_ks);
+                qb[d] = __ldg(bs_row + kk * bs_ks);
             }
 #pragma unroll 4
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -313,8 +332,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 for (int d = 0; d + 1 < PF; ++d) { qa[d] = qa[d + 1]; qb[d] = qb[d + 1]; }
                 {
                     const int kk = min(kb + PF, kb1 - 1);
-                    qa[PF - 1] = __ldg(as_row + kk);
-                    qb[PF - 1] = __ldg(bs_row + kk);
+                    qa[PF - 1] = __ldg(as_row + kk * as_ks);
+                    qb[PF - 1] = __ldg(bs_row + kk * bs_ks);
                 }
                 const float2 s2 = make_float2(s, s);
                 const int buf = it % NBUF;
@@ -452,6 +471,8 @@ splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restric
 using Cfg128 = GemmCfg<128, 6>;
 using Cfg256 = GemmCfg<256, 4>;
 using CfgPair = GemmCfg<256, 6, true>;      // 256 x 256 tile per CTA pair
+using Cfg128Mn = GemmCfg<128, 6, false, true>;
+using Cfg256Mn = GemmCfg<256, 4, false, true>;
 
 template <class Cfg>
 cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
@@ -509,20 +530,29 @@ cudaError_t fp8_gemm_prepare_device() {
     e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg256::kSmemBytes);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(fp8_gemm_kernel<CfgPair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                CfgPair::kSmemBytes);
+    e = cudaFuncSetAttribute(fp8_gemm_kernel<CfgPair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             CfgPair::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg128Mn>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg128Mn::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256Mn>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Cfg256Mn::kSmemBytes);
 }
 
 cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
                             const CUtensorMap& tma_p, const GemmDestMaps* dests, const GemmParams& p, int block_n,
-                            int num_sms, cudaStream_t stream) {
+                            int num_sms, cudaStream_t stream, bool mn_major) {
     GemmDestMaps local;
     if (!dests) {
         for (int i = 0; i < 8; ++i) local.m[i] = tma_c;
         dests = &local;
     }
     // block_n: 128 / 256 = one-CTA tiles of that width; 512 = the CTA-pair configuration (256 x 256 per pair)
-    cudaError_t e = block_n == 512   ? launch_cfg<CfgPair>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
+    cudaError_t e = mn_major
+                        ? (block_n == 256 ? launch_cfg<Cfg256Mn>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
+                                          : launch_cfg<Cfg128Mn>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream))
+                    : block_n == 512 ? launch_cfg<CfgPair>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
                     : block_n == 256 ? launch_cfg<Cfg256>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
                                      : launch_cfg<Cfg128>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream);
     if (e != cudaSuccess) return e;

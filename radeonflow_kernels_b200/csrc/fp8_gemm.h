@@ -15,6 +15,9 @@ struct GemmParams {
     int* status;            // device status word (0 = ok)
     int m, n, k;
     int tiles_m, tiles_n, splits;
+    // Scale addressing: a_scale[row * as_row_stride + kb * as_k_stride] (row-major [m, k/128]: (k/128, 1);
+    // the reference's physical layout [k/128][m]: (1, m)); same for b_scale with its block row.
+    long long as_row_stride, as_k_stride, bs_row_stride, bs_k_stride;
     int n_dest;             // copies of C to write (1, or the number of GPUs of an N-split GEMM)
     int c_col_offset;       // column of this GEMM's C inside each destination matrix
 };
@@ -35,9 +38,11 @@ inline int gemm_b_box_rows(int block_n) { return block_n == 512 ? 128 : block_n;
 // `tma_c` stores bf16 C boxes of 32 rows x 64 columns; `tma_p` (used when p.splits > 1) stores fp32
 // slice boxes of 32 rows x 32 columns into the [splits][m][n] scratch.
 // When p.n_dest > 1, `dests` holds p.n_dest maps and replaces tma_c (split-K is not combined with it).
+// `mn_major`: A and B are stored [k][m] / [k][n] (the reference's physical layout); their tensor maps then
+// have boxes of 128 K-rows x 128 elements of M/N and block_n must be 128 or 256.
 cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
                             const CUtensorMap& tma_p, const GemmDestMaps* dests, const GemmParams& p, int block_n,
-                            int num_sms, cudaStream_t stream);
+                            int num_sms, cudaStream_t stream, bool mn_major = false);
 
 // Sets the launch attributes of every GEMM kernel configuration on the current device (normally done
 // lazily by the first launch of each configuration).

@@ -123,6 +123,8 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
     p.tiles_m = (m + rf::gemm_tile_rows(bn) - 1) / rf::gemm_tile_rows(bn);
     p.tiles_n = (n + rf::gemm_tile_cols(bn) - 1) / rf::gemm_tile_cols(bn);
     p.splits = splits;
+    p.as_row_stride = k / 128; p.as_k_stride = 1;
+    p.bs_row_stride = k / 128; p.bs_k_stride = 1;
     p.n_dest = 1;
     p.c_col_offset = 0;
     cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, nullptr, p, bn, sd->num_sms,

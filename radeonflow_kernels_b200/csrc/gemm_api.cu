@@ -51,8 +51,7 @@ GemmPlan plan_for(int m, int n, int k, int num_sms, int bn, int forced_split) {
     const int tiles = ((m + tr - 1) / tr) * ((n + tc - 1) / tc);
     const int kb = k / kBlockK;
     if (bn == 512) num_sms /= 2;     // work items go to CTA pairs
-    // measured cycles per K block of one work item / 256: 128x128 ~ 660, 128x256 ~ 790, pair 256x256 ~ 700
-    const double tile_w = bn == 512 ? 2.7 : (bn == 256 ? 3.1 : 2.6);
+    const double tile_w = bn == 512 ? 2.3 : bn / 128.0;   // relative time of one K block of one work item
     GemmPlan best{bn, 1, 1e30};
     for (int s = 1; s <= 8; ++s) {
         if (forced_split > 0 && s != forced_split) continue;
@@ -60,7 +59,7 @@ GemmPlan plan_for(int m, int n, int k, int num_sms, int bn, int forced_split) {
         if (s > kb) break;
         const int rounds = (tiles * s + num_sms - 1) / num_sms;
         const int kb_per = (kb + s - 1) / s;
-        double cost = (double)rounds * (kb_per * tile_w + 8.0);
+        double cost = (double)rounds * (kb_per * tile_w + 4.0);
         if (s > 1) {
             const double bytes = 8.0 * s * (double)m * n + 2.0 * (double)m * n;
             cost += (bytes / 6.0e12 + 2.5e-6) / 0.14e-6;
@@ -90,8 +89,10 @@ GemmPlan choose_plan(int m, int n, int k, int num_sms, int forced_split) {
 // `col_offset` of each of the n_dest row-major [m, dest_n] matrices in dest_c (N-split GEMM) and `c` is unused.
 int gemm_impl(const void* a, const void* b, const float* as, const float* bs, void* c, int m, int n, int k,
               int split_k, void* workspace, size_t workspace_bytes, bool own_workspace, cudaStream_t stream,
-              void* const* dest_c = nullptr, int n_dest = 1, int dest_n = 0, int col_offset = 0) {
+              void* const* dest_c = nullptr, int n_dest = 1, int dest_n = 0, int col_offset = 0,
+              bool mn_major = false) {
     if (!shape_ok(m, n, k)) return RF_ERR_BAD_SHAPE;
+    if (mn_major && (m % 16) != 0) return RF_ERR_BAD_SHAPE;     // [k][m] rows must be 16-byte multiples for TMA
     if (n_dest > 1) {
         if (!dest_c || n_dest > 8 || dest_n < col_offset + n || dest_n % 8 != 0 || col_offset % 64 != 0)
             return RF_ERR_BAD_SHAPE;
@@ -108,7 +109,8 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
 
     const int kb = k / kBlockK;
     if (split_k > kb) split_k = kb;
-    const GemmPlan plan = choose_plan(m, n, k, st->num_sms, split_k);
+    GemmPlan plan = choose_plan(m, n, k, st->num_sms, split_k);
+    if (mn_major && plan.block_n == 512) plan = plan_for(m, n, k, st->num_sms, 256, split_k);
     const int bn = plan.block_n;
     const int splits = plan.splits;
 
@@ -126,12 +128,21 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     }
 
     CUtensorMap ta, tb;
-    if (!rf::encode_tma_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)m, (uint64_t)k, (uint64_t)k, 128, 128,
-                           true))
-        return RF_ERR_CUDA;
-    if (!rf::encode_tma_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k, (uint64_t)k,
-                           (uint32_t)rf::gemm_b_box_rows(bn), 128, true))
-        return RF_ERR_CUDA;
+    if (mn_major) {
+        // a [k][m], b [k][n]: boxes of 128 K-rows x 128 bytes of M / N
+        if (!rf::encode_tma_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)k, (uint64_t)m, (uint64_t)m, 128,
+                               128, true) ||
+            !rf::encode_tma_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)k, (uint64_t)n, (uint64_t)n, 128,
+                               128, true))
+            return RF_ERR_CUDA;
+    } else {
+        if (!rf::encode_tma_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)m, (uint64_t)k, (uint64_t)k, 128,
+                               128, true))
+            return RF_ERR_CUDA;
+        if (!rf::encode_tma_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k, (uint64_t)k,
+                               (uint32_t)rf::gemm_b_box_rows(bn), 128, true))
+            return RF_ERR_CUDA;
+    }
 
     CUtensorMap tc, tp;
     if (!rf::encode_tma_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, (uint64_t)m, (uint64_t)n, (uint64_t)n * 2, 32,
@@ -155,6 +166,13 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     p.tiles_m = (m + rf::gemm_tile_rows(bn) - 1) / rf::gemm_tile_rows(bn);
     p.tiles_n = (n + rf::gemm_tile_cols(bn) - 1) / rf::gemm_tile_cols(bn);
     p.splits = splits;
+    if (mn_major) {
+        p.as_row_stride = 1; p.as_k_stride = m;
+        p.bs_row_stride = 1; p.bs_k_stride = (n + 127) / 128;
+    } else {
+        p.as_row_stride = kb; p.as_k_stride = 1;
+        p.bs_row_stride = kb; p.bs_k_stride = 1;
+    }
     p.n_dest = n_dest;
     p.c_col_offset = col_offset;
     rf::GemmDestMaps dests;
@@ -166,7 +184,8 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
                 return RF_ERR_CUDA;
         }
     }
-    cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, n_dest > 1 ? &dests : nullptr, p, bn, st->num_sms, stream);
+    cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, n_dest > 1 ? &dests : nullptr, p, bn, st->num_sms, stream,
+                                        mn_major);
     if (e != cudaSuccess) {
         fprintf(stderr, "rf_b200: fp8 gemm launch failed: %s\n", cudaGetErrorString(e));
         return RF_ERR_CUDA;
@@ -236,6 +255,12 @@ int rf_fp8_gemm_nsplit(const void* a, const void* b_shard, const float* as, cons
                          reinterpret_cast<cudaStream_t>(stream));
     return gemm_impl(a, b_shard, as, bs_shard, nullptr, m, n_loc, k, 1, nullptr, 0, true,
                      reinterpret_cast<cudaStream_t>(stream), c_all, world, n_total, rank * n_loc);
+}
+
+int rf_fp8_gemm_colmajor(const void* a, const void* b, const float* as, const float* bs, void* c, int m, int n,
+                         int k, void* workspace, size_t workspace_bytes, rf_stream_t stream) {
+    return gemm_impl(a, b, as, bs, c, m, n, k, 0, workspace, workspace_bytes, workspace == nullptr,
+                     reinterpret_cast<cudaStream_t>(stream), nullptr, 1, 0, 0, true);
 }
 
 void run(void* a, void* b, void* as, void* bs, void* c, int m, int n, int k, PerfMetrics* metrics,

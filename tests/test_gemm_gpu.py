@@ -183,3 +183,35 @@ print("PAIR OK")
     env = dict(os.environ, RF_FP8_GEMM_BN="512", RF_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "PAIR OK" in res.stdout, (res.stdout + res.stderr)[-3000:]
+
+
+@pytest.mark.parametrize("m,n,k,seed", [(64, 64, 128, 6635), (64, 576, 7168, 542), (96, 7168, 256, 1234),
+                                         (128, 512, 7168, 2514), (512, 4096, 512, 543), (1024, 1536, 7168, 8135),
+                                         (6144, 576, 7168, 9863), (1040, 320, 1024, 3)])
+def test_reference_physical_layout_entry(rf_lib, m, n, k, seed):
+    """`rf_fp8_gemm_colmajor`: operands as the reference stores them ([k][m], [k][n], scales [k/128][m] and
+    [k/128][n/128]); same result as the oracle on the logical matrices."""
+    a, b, a_s, b_s = o.generate_input(m, n, k, seed, "randn")
+    from tests.helpers import to_dev
+    da = to_dev(np.ascontiguousarray(a.T))
+    db = to_dev(np.ascontiguousarray(b.T))
+    das = to_dev(np.ascontiguousarray(a_s.T))
+    dbs = to_dev(np.ascontiguousarray(b_s.T))
+    full, c = canary_output(m, n)
+    st = rf_lib.rf_fp8_gemm_colmajor(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(), c.data_ptr(),
+                                     m, n, k, None, 0, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    assert canary_intact(full, m, n)
+    assert_close(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a, b, a_s, b_s))
+
+
+def test_reference_physical_layout_rejects_unaligned_m(rf_lib):
+    a, b, a_s, b_s = o.generate_input(72, 64, 128, 1)
+    from tests.helpers import to_dev
+    c = torch.empty((72, 64), dtype=torch.bfloat16, device="cuda:0")
+    st = rf_lib.rf_fp8_gemm_colmajor(to_dev(np.ascontiguousarray(a.T)).data_ptr(), to_dev(b.T.copy()).data_ptr(),
+                                     to_dev(a_s.T.copy()).data_ptr(), to_dev(b_s.T.copy()).data_ptr(), c.data_ptr(),
+                                     72, 64, 128, None, 0, None)
+    assert st == 1
