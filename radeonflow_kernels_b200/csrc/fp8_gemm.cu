@@ -132,6 +132,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     constexpr bool TWO = Cfg::kTwoCta;
+#ifdef RF_SINGLE_ISSUE
+    constexpr bool kDualIssue = false;
+#else
+    constexpr bool kDualIssue = !TWO && (NBUF % 2 == 0);
+#endif
     const uint32_t cta_rank = TWO ? cluster_ctarank() : 0u;      // 0 = leader of the pair
     const int unit = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;          // work-loop index
     const int unit_stride = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -213,8 +218,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             }
         }
         if (lane == 0) { RF_STAT_FLUSH(0, w_empty); }
-    } else if (warp == 1) {
-        // -------------------------------------------------------- MMA issuer
+    } else if (warp == 1 || (kDualIssue && warp == 2)) {
+        // ------------------------------------------------------- MMA issuers
+        // Issuing one K block (two barrier waits, four MMAs, one commit) is a serial chain of a few
+        // hundred cycles in a single thread, about as long as the MMAs take to execute.  Two warps on
+        // different schedulers therefore alternate K blocks: even blocks (and the even TMEM buffers)
+        // belong to warp 1, odd ones to warp 2.  Blocks are independent (separate accumulator buffers
+        // and smem stages), so no ordering between the two issuers is needed.
+        const uint32_t my_parity = (uint32_t)(warp - 1);
         constexpr uint32_t idesc = make_idesc(TWO ? 2 * BM : BM, BN, /*e4m3*/ 0, /*e4m3*/ 0,
                                               Cfg::kMnMajor ? 1 : 0, Cfg::kMnMajor ? 1 : 0);
         // descriptor advance per MMA (K = 32): 32 bytes inside the swizzled row for K-major operands,
@@ -232,6 +243,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 const uint32_t ph = (it / STAGES) & 1;
                 const int buf = it % NBUF;
                 const uint32_t bph = (it / NBUF) & 1;
+                if (kDualIssue && (it & 1u) != my_parity) continue;
                 if (TWO && cta_rank != 0) {
                     // Second CTA of the pair: it issues no MMA.  This warp relays "my stage has landed"
                     // to the leader (a TMA load can only signal a barrier of the CTA it writes to).
@@ -309,7 +321,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const bool nb_ok = col0 < p.n;
             const float* as_row = p.a_scale + (size_t)(row_ok ? row : 0) * p.as_row_stride;
             const float* bs_row = p.b_scale + (size_t)(nb_ok ? nb : 0) * p.bs_row_stride;
-            const long long as_ks = p.as_k_stride, bs_ks = p.bs_k_stride;
+            // K-major scale tables have unit stride along K (a compile-time fact the address arithmetic
+            // of the prefetch queue depends on); only the reference's [k/128][m] tables stride by m
+            const int as_ks = Cfg::kMnMajor ? (int)p.as_k_stride : 1;
+            const int bs_ks = Cfg::kMnMajor ? (int)p.bs_k_stride : 1;
 
             float2 acc[CPT / 2];
 #pragma unroll
