@@ -350,6 +350,39 @@ def run_extras(args, rank, world, dev, dist, peaks):
     return out
 
 
+def run_moe_only(args):
+    """Single-GPU MoE layer (config 3) alone: W warm-up layers, K timed layers, one JSON line."""
+    import torch
+    from radeonflow_kernels_b200 import moe as M, build
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    build.build()
+    L = _lib_handle()
+    d, f, e, k, t = 7168, 2048, 32, 4, 8192
+    w = make_moe_weights(torch, dev, d, f, list(range(e)), 11, with_router_for=e)
+    cfg = {"d_hidden": d, "d_expert": f, "n_routed_experts": e, "n_shared_experts": 1, "n_experts_per_token": k,
+           "batch_size": 1, "seq_len": t}
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    x = torch.randn((1, t, d), device=dev, dtype=torch.float16, generator=g)
+    buf = M.MoEBuffers(x, w, cfg)
+    sp = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    steps = min(args.steps, 50)
+    ms = _timed(lambda: L.rf_moe_forward(ctypes.byref(buf.raw), None, sp, None), steps, max(3, args.warmup), dev, 1,
+                None)
+    fl = moe_layer_flops(t, d, f, e, k)
+    peaks = measured_peaks()
+    print(json.dumps({
+        "metric": "moe_layer_tokens_per_s", "value": t / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16 x fp16 -> f32", "data": "synthetic",
+        "config": {"workload": "MoE layer T=8192 d=7168 f=2048 E=32 top-4 + 1 shared (weights 3 GB > L2)"},
+        "roofline": {"bound": "tensor", "achieved": fl / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "traffic": None,
+                     "kernel": "moe_gemm_kernel"},
+        "gpu_launches": 18 * steps}), flush=True)
+
+
 def _lib_handle():
     from radeonflow_kernels_b200 import _lib
     return _lib.lib()
@@ -584,6 +617,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE and N-split GEMM workloads")
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "moe"],
+                    help="sweep = the FP8 GEMM benchmark line (default); moe = only the single-GPU MoE layer "
+                         "(profiling aid: prints its own line, metric moe_layer_tokens_per_s)")
     ap.add_argument("--shapes", default="", help="restrict the sweep, e.g. 6144x4608x7168,1024x512x7168 "
                                                  "(profiling aid; the JSON line names the restricted workload)")
     args = ap.parse_args()
@@ -595,6 +631,8 @@ def main():
         SWEEP = [tuple(int(v) for v in t.split("x")) for t in args.shapes.split(",")]
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "moe":
+        run_moe_only(args)
     else:
         run_gpu_arm(args)
 
