@@ -47,6 +47,20 @@ __device__ __forceinline__ float silu_fp16_rounded(float g) {
     return __half2float(__float2half_rn(s));
 }
 
+// Work item -> (row tile, column block).  Items walk 8 consecutive row tiles (about one expert's rows)
+// for one column block, then the next column block of the same 8 tiles: CTAs running at the same time
+// share the weight column block (read from HBM once per expert and chunk) while the 8 A tiles stay in
+// L2 across all column blocks.
+__device__ __forceinline__ void decode_item(int w, int n_tiles, int nbn, int* tile, int* nb) {
+    constexpr int GROUP = 8;
+    const int chunk = w / (GROUP * nbn);
+    const int first = chunk * GROUP;
+    const int rows = min(GROUP, n_tiles - first);
+    const int r = w - chunk * GROUP * nbn;
+    *nb = r / rows;
+    *tile = first + r % rows;
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_out,
@@ -100,8 +114,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         uint32_t it = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-            const int tile = w / nbn;
-            const int n0 = (w - tile * nbn) * TILE_N;
+            int tile, nb_i;
+            decode_item(w, n_tiles, nbn, &tile, &nb_i);
+            const int n0 = nb_i * TILE_N;
             const int row0 = __ldg(p.tile_row0 + tile);
             const int grp = __ldg(p.tile_group + tile);
             const CUtensorMap* mb = p.b_maps + grp;
@@ -179,8 +194,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         uint32_t tcount = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tcount) {
-            const int tile = w / nbn;
-            const int n0 = (w - tile * nbn) * TILE_N;
+            int tile, nb_i;
+            decode_item(w, n_tiles, nbn, &tile, &nb_i);
+            const int n0 = nb_i * TILE_N;
             const int row0 = __ldg(p.tile_row0 + tile);
             const int grp = __ldg(p.tile_group + tile);
             const int row_end = __ldg(p.group_offsets + grp + 1);
