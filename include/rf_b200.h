@@ -298,6 +298,17 @@ int rf_peer_free(void *ptr);
 int rf_fp8_gemm_nsplit(const void *a, const void *b_shard, const float *as, const float *bs_shard,
                        void *const *c_all, int m, int n_total, int k, int rank, int world, rf_stream_t stream);
 
+/* Rendezvous of the ranks of one node through peer memory, stream-ordered: every rank raises its flag
+ * (the monotonically increasing `epoch` >= 1) in every peer's sync area and waits, for at most two
+ * seconds, until all peers have raised theirs; work queued before it on any rank (peer stores
+ * included) is complete before work queued after it on every rank.  With counts_dev != NULL the
+ * n_counts int32 values are first all-gathered into row `rank` of every peer's gather area.
+ * sync_all[r] = rank r's sync area as mapped here: int32 [8 + world * n_counts], zero before epoch 1;
+ * the gathered matrix starts at word 8.  A wait that expires sets the device status word
+ * (rf_device_status) and the kernel returns.  One launch per rank, each rank on its own GPU.     */
+int rf_moe_ep_rendezvous(void *const *sync_all, const int *counts_dev, int n_counts, int rank, int world,
+                         int epoch, rf_stream_t stream);
+
 /* Expert-parallel layout: from the all-gathered pair counts counts_all_dev [world][n_experts]
  * computes, on the device, where this rank's rows land in the owners' receive buffers
  * (send_base_dev [n_experts]) and the row ranges of this rank's own experts

@@ -4,6 +4,7 @@
 // combine reads the expert outputs straight from the owner GPUs (combine).  Only ordinary peer
 // loads and stores are used; ordering between GPUs comes from stream-ordered barriers outside.
 #include "moe_kernels.h"
+#include "ptx.cuh"
 
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -122,7 +123,47 @@ ep_combine_kernel(PeerPtrs y, const uint4* __restrict__ shared_out, const int* _
     }
 }
 
+// One block.  Threads publish this rank's counts to every peer, then thread s < world raises this
+// rank's flag on peer s and waits for peer s's flag here.  Flags only grow (epoch numbers), so a slow
+// rank can never be overtaken by two epochs.  The wait is bounded: on expiry the status word is set
+// and the kernel returns.
+__global__ void __launch_bounds__(256)
+ep_rendezvous_kernel(PeerPtrs sync, const int* __restrict__ counts, int n_counts, int rank, int world, int epoch,
+                     int* status) {
+    if (counts != nullptr) {
+        for (int i = threadIdx.x; i < n_counts * world; i += blockDim.x) {
+            const int peer = i / n_counts;
+            const int j = i - peer * n_counts;
+            int* area = static_cast<int*>(pick_peer(sync, peer));
+            area[8 + rank * n_counts + j] = counts[j];
+        }
+    }
+    __threadfence_system();          // the counts (and every earlier peer store of this stream) before the flag
+    __syncthreads();
+    if (threadIdx.x < world) {
+        const int peer = threadIdx.x;
+        volatile int* theirs = static_cast<int*>(pick_peer(sync, peer)) + rank;
+        *theirs = epoch;
+        volatile int* mine = static_cast<int*>(pick_peer(sync, rank)) + peer;
+        const unsigned long long t0 = globaltimer_ns();
+        unsigned spins = 0;
+        while (*mine < epoch) {
+            if ((++spins & 0x3ff) == 0 && globaltimer_ns() - t0 > kWaitTimeoutNs) {
+                atomicCAS(status, 0, kErrSchedWait);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+}
+
 }  // namespace
+
+cudaError_t moe_ep_rendezvous_launch(const PeerPtrs& sync, const int* counts, int n_counts, int rank, int world,
+                                     int epoch, int* status, cudaStream_t stream) {
+    ep_rendezvous_kernel<<<1, 256, 0, stream>>>(sync, counts, n_counts, rank, world, epoch, status);
+    return cudaGetLastError();
+}
 
 cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int n_experts, int* send_base,
                                  int* recv_offsets, cudaStream_t stream) {

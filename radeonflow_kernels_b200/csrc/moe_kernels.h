@@ -42,6 +42,14 @@ cudaError_t moe_ep_combine_launch(const PeerPtrs& y, const void* shared_out, con
                                   const int* pair_rank, const int* pair_row, int n_tokens, int top_k, int row_bytes,
                                   void* out, cudaStream_t stream);
 
+// Cross-GPU rendezvous through peer memory.  `sync` = every rank's sync area (int32): words [0, 8) are
+// arrival flags (slot s is written by rank s), words [8, 8 + world * n_counts) an all-gather area.
+// Each rank stores `epoch` into its slot on every peer and waits (bounded) until its own slots hold
+// `epoch`; with `counts` != nullptr it first publishes its n_counts values into row `rank` of every
+// peer's gather area.  One launch per rank, every rank on its own GPU.
+cudaError_t moe_ep_rendezvous_launch(const PeerPtrs& sync, const int* counts, int n_counts, int rank, int world,
+                                     int epoch, int* status, cudaStream_t stream);
+
 // ---- grouped fp16 GEMM (moe_gemm.cu)
 enum MoeGemmMode {
     kMoeGemmPlain = 0,    // out[r, n] = fp16(X[r,:] . W_g[:, n]); W_g is [K, N] row-major (N contiguous)

@@ -42,6 +42,21 @@ int rf_peer_free(void* ptr) {
     return cudaFree(ptr) == cudaSuccess ? RF_OK : RF_ERR_CUDA;
 }
 
+int rf_moe_ep_rendezvous(void* const* sync_all, const int* counts_dev, int n_counts, int rank, int world, int epoch,
+                         rf_stream_t stream) {
+    if (!sync_all) return RF_ERR_NULL_POINTER;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || n_counts < 0 || epoch <= 0) return RF_ERR_BAD_SHAPE;
+    rf::DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    rf::PeerPtrs pp;
+    for (int i = 0; i < 8; ++i) pp.p[i] = sync_all[i < world ? i : 0];
+    for (int i = 0; i < world; ++i)
+        if (!pp.p[i] || ((uintptr_t)pp.p[i] & 15)) return RF_ERR_NULL_POINTER;
+    return rf::moe_ep_rendezvous_launch(pp, counts_dev, counts_dev ? n_counts : 0, rank, world, epoch, st->status,
+                                        reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? RF_OK : RF_ERR_CUDA;
+}
+
 int rf_moe_ep_layout(const int* counts_all_dev, int rank, int world, int n_experts, int* send_base_dev,
                      int* recv_offsets_dev, rf_stream_t stream) {
     if (!counts_all_dev || !send_base_dev || !recv_offsets_dev) return RF_ERR_NULL_POINTER;

@@ -4,8 +4,9 @@
   column slab of C into every rank's full C over NVLink (the all-gather is part of the kernel).
 * ``ExpertParallelMoE`` - the MoE layer with experts sharded ``E / world`` per rank; tokens are
   dispatched by peer stores into the owner's receive buffer and expert outputs are combined by
-  peer loads.  ``torch.distributed`` (NCCL) carries only the control traffic: a [world, E] count
-  all-gather and one-element all-reduces that act as stream-ordered barriers.
+  peer loads.  The per-step control traffic (a [world, E] count all-gather and two barriers) also
+  goes through peer memory (``rf_moe_ep_rendezvous``); ``torch.distributed`` (NCCL) is used at set-up
+  to exchange the IPC handles, and by the N-split GEMM for its completion barrier.
 
 The reference is single-GPU (no collective call anywhere in it); these are additions on top of
 its operator boundary, built from the same C-ABI stage entry points.
@@ -195,7 +196,7 @@ class ExpertParallelMoE:
         self.exp_w = e((T * K,), f16)
         self.pair_rank = e((T * K,), i32)
         self.pair_row = e((T * K,), i32)
-        self.counts_all = e((self.world * E,), i32)
+        self.counts = e((E,), i32)
         self.send_base = e((E,), i32)
         self.recv_offsets = e((self.E_loc + 1,), i32)
         self.single_offsets = torch.tensor([0, T], dtype=i32, device=dev)
@@ -209,6 +210,14 @@ class ExpertParallelMoE:
         self.side_stream = torch.cuda.Stream(device=dev)
         self.ev_ready = torch.cuda.Event()
         self.ev_sent = torch.cuda.Event()
+        # sync area: 8 arrival flags + the [world, E] count matrix, zeroed before the first epoch
+        self.sync = PeerBuffer(4 * (8 + self.world * E), dev, group)
+        self.sync.tensor(torch.int32, (8 + self.world * E,)).zero_()
+        self.counts_all = self.sync.tensor(torch.int32, (8 + self.world * E,))[8:]
+        self.epoch = 0
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=group)           # every rank's sync area is zero before anyone raises a flag
         self.recv_x = PeerBuffer(self.capacity * d * 2, dev, group)
         self.y = PeerBuffer(self.capacity * d * 2, dev, group)
 
@@ -237,12 +246,10 @@ class ExpertParallelMoE:
                              self.perm_experts.data_ptr(), self.perm_rows.data_ptr(), self.first.data_ptr(),
                              self.rev.data_ptr(), self.exp_w.data_ptr(), self.sort_scratch.data_ptr(), s),
             "rf_moe_permute")
-        counts = self.first[1:] - self.first[:-1]
-        if self.world > 1:
-            # also orders this step after every rank's previous combine (its reads of our y buffer)
-            dist.all_gather_into_tensor(self.counts_all, counts.contiguous(), group=self.group)
-        else:
-            self.counts_all.copy_(counts)
+        # pair counts per global expert, all-gathered through peer memory; the rendezvous also orders this
+        # step after every rank's previous combine (its reads of our y buffer)
+        torch.sub(self.first[1:], self.first[:-1], out=self.counts)
+        self._rendezvous(self.counts.data_ptr(), E)
         chk(L.rf_moe_ep_layout(self.counts_all.data_ptr(), self.rank, self.world, E, self.send_base.data_ptr(),
                                self.recv_offsets.data_ptr(), s), "rf_moe_ep_layout")
         # Dispatch runs on a side stream; the shared expert, which needs no exchange, runs on the main
@@ -262,16 +269,21 @@ class ExpertParallelMoE:
         chk(L.rf_moe_grouped_gemm(self.sh1.data_ptr(), T, self._s_down, None, self.single_offsets.data_ptr(), 1, d,
                                   self.fs, self.sh2.data_ptr(), s), "shared fc2")
         main.wait_event(self.ev_sent)
-        stream_barrier(self.flag, self.group)          # every rank's dispatch has landed
+        self._rendezvous(None, 0)                       # every rank's dispatch has landed
         chk(L.rf_moe_grouped_gemm(self.recv_x.local_ptr, self.capacity, self._w_gate, self._w_up,
                                   self.recv_offsets.data_ptr(), self.E_loc, f, d, self.h.data_ptr(), s), "routed fc1")
         chk(L.rf_moe_grouped_gemm(self.h.data_ptr(), self.capacity, self._w_down, None, self.recv_offsets.data_ptr(),
                                   self.E_loc, d, f, self.y.local_ptr, s), "routed fc2")
-        stream_barrier(self.flag, self.group)          # every rank's expert outputs are complete
+        self._rendezvous(None, 0)                       # every rank's expert outputs are complete
         chk(L.rf_moe_ep_combine(self.y.ptr_array, self.sh2.data_ptr(), self.rev.data_ptr(), self.exp_w.data_ptr(),
                                 self.pair_rank.data_ptr(), self.pair_row.data_ptr(), T, K, d, self.world,
                                 self.out.data_ptr(), s), "rf_moe_ep_combine")
         return self.out
+
+    def _rendezvous(self, counts_ptr, n_counts):
+        self.epoch += 1
+        _lib.check(_lib.lib().rf_moe_ep_rendezvous(self.sync.ptr_array, counts_ptr, n_counts, self.rank, self.world,
+                                                   self.epoch, _stream()), "rf_moe_ep_rendezvous")
 
     def received_rows(self) -> int:
         """Rows this rank's experts processed in the last forward (synchronises)."""
@@ -280,3 +292,4 @@ class ExpertParallelMoE:
     def close(self):
         self.recv_x.close()
         self.y.close()
+        self.sync.close()
