@@ -298,6 +298,10 @@ int rf_peer_free(void *ptr);
 int rf_fp8_gemm_nsplit(const void *a, const void *b_shard, const float *as, const float *bs_shard,
                        void *const *c_all, int m, int n_total, int k, int rank, int world, rf_stream_t stream);
 
+/* out[r, :] = fp16(out[r, :] + add[r, :]) for fp16 [n_rows, d_hidden] (the "+ shared[t]" of
+ * reduce_output, src/moe/moe_topk_kernel.cpp:249, as a separate pass).                         */
+int rf_moe_add_rows(void *out, const void *add, int n_rows, int d_hidden, rf_stream_t stream);
+
 /* Rendezvous of the ranks of one node through peer memory, stream-ordered: every rank raises its flag
  * (the monotonically increasing `epoch` >= 1) in every peer's sync area and waits, for at most two
  * seconds, until all peers have raised theirs; work queued before it on any rank (peer stores
@@ -325,7 +329,9 @@ int rf_moe_ep_dispatch(const void *x, const int *permuted_experts, const int *pe
                        rf_stream_t stream);
 
 /* Combine: reduce_output (src/moe/moe_topk_kernel.cpp:215-251) reading each expert output row
- * from its owner rank's `y_all[r]` (fp16 [capacity, d_hidden]) over NVLink.                   */
+ * from its owner rank's `y_all[r]` (fp16 [capacity, d_hidden]) over NVLink.  shared_fc2_output
+ * may be NULL: the shared expert's rows are then added afterwards with rf_moe_add_rows, which
+ * lets its second GEMM run while the combine is pulling rows over NVLink.                     */
 int rf_moe_ep_combine(void *const *y_all, const void *shared_fc2_output, const int *rev_permuted_rows,
                       const void *expanded_seq_softmax, const int *pair_rank, const int *pair_row, int n_tokens,
                       int top_k, int d_hidden, int world, void *final_output, rf_stream_t stream);

@@ -138,6 +138,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_peer_free.argtypes = [vp]
     L.rf_fp8_gemm_nsplit.restype = ci
     L.rf_fp8_gemm_nsplit.argtypes = [vp, vp, vp, vp, pvp, ci, ci, ci, ci, ci, vp]
+    L.rf_moe_add_rows.restype = ci
+    L.rf_moe_add_rows.argtypes = [vp, vp, ci, ci, vp]
     L.rf_moe_ep_rendezvous.restype = ci
     L.rf_moe_ep_rendezvous.argtypes = [pvp, vp, ci, ci, ci, ci, vp]
     L.rf_moe_ep_layout.restype = ci

@@ -110,7 +110,8 @@ ep_combine_kernel(PeerPtrs y, const uint4* __restrict__ shared_out, const int* _
                 acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
             }
         }
-        const uint4 sq = __ldg(shared_out + (size_t)t * vec_per_row + v);
+        uint4 sq = make_uint4(0u, 0u, 0u, 0u);                 // fp16 zeros when the shared expert is added later
+        if (shared_out != nullptr) sq = __ldg(shared_out + (size_t)t * vec_per_row + v);
         const __half2* sh = reinterpret_cast<const __half2*>(&sq);
         uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
@@ -120,6 +121,25 @@ ep_combine_kernel(PeerPtrs y, const uint4* __restrict__ shared_out, const int* _
             oh[j] = __floats2half2_rn(acc[2 * j] + f.x, acc[2 * j + 1] + f.y);
         }
         out[(size_t)t * vec_per_row + v] = o;
+    }
+}
+
+// out += add, fp16 rows, fp32 arithmetic (the shared expert's output joins the combined routed output
+// when its second GEMM ran concurrently with the combine)
+__global__ void __launch_bounds__(256)
+add_rows_kernel(uint4* __restrict__ out, const uint4* __restrict__ add, size_t n_vec) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+        uint4 a = out[i];
+        const uint4 b = __ldg(add + i);
+        __half2* ah = reinterpret_cast<__half2*>(&a);
+        const __half2* bh = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 x = __half22float2(ah[j]);
+            const float2 y = __half22float2(bh[j]);
+            ah[j] = __floats2half2_rn(x.x + y.x, x.y + y.y);
+        }
+        out[i] = a;
     }
 }
 
@@ -162,6 +182,17 @@ ep_rendezvous_kernel(PeerPtrs sync, const int* __restrict__ counts, int n_counts
 cudaError_t moe_ep_rendezvous_launch(const PeerPtrs& sync, const int* counts, int n_counts, int rank, int world,
                                      int epoch, int* status, cudaStream_t stream) {
     ep_rendezvous_kernel<<<1, 256, 0, stream>>>(sync, counts, n_counts, rank, world, epoch, status);
+    return cudaGetLastError();
+}
+
+cudaError_t moe_add_rows_launch(void* out, const void* add, size_t n_elems, int num_sms, cudaStream_t stream) {
+    const size_t n_vec = n_elems / 8;
+    if (n_vec == 0) return cudaSuccess;
+    size_t blocks = (n_vec + 255) / 256;
+    const size_t cap = (size_t)num_sms * 8;
+    if (blocks > cap) blocks = cap;
+    add_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<uint4*>(out), static_cast<const uint4*>(add),
+                                                         n_vec);
     return cudaGetLastError();
 }
 

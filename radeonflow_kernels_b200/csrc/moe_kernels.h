@@ -42,6 +42,9 @@ cudaError_t moe_ep_combine_launch(const PeerPtrs& y, const void* shared_out, con
                                   const int* pair_rank, const int* pair_row, int n_tokens, int top_k, int row_bytes,
                                   void* out, cudaStream_t stream);
 
+// out[i] = fp16(out[i] + add[i]) over n_elems fp16 values (n_elems % 8 == 0)
+cudaError_t moe_add_rows_launch(void* out, const void* add, size_t n_elems, int num_sms, cudaStream_t stream);
+
 // Cross-GPU rendezvous through peer memory.  `sync` = every rank's sync area (int32): words [0, 8) are
 // arrival flags (slot s is written by rank s), words [8, 8 + world * n_counts) an all-gather area.
 // Each rank stores `epoch` into its slot on every peer and waits (bounded) until its own slots hold

@@ -42,6 +42,16 @@ int rf_peer_free(void* ptr) {
     return cudaFree(ptr) == cudaSuccess ? RF_OK : RF_ERR_CUDA;
 }
 
+int rf_moe_add_rows(void* out, const void* add, int n_rows, int d_hidden, rf_stream_t stream) {
+    if (!out || !add) return RF_ERR_NULL_POINTER;
+    if (n_rows < 0 || d_hidden <= 0 || d_hidden % 8 != 0) return RF_ERR_BAD_SHAPE;
+    rf::DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    return rf::moe_add_rows_launch(out, add, (size_t)n_rows * d_hidden, st->num_sms,
+                                   reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? RF_OK : RF_ERR_CUDA;
+}
+
 int rf_moe_ep_rendezvous(void* const* sync_all, const int* counts_dev, int n_counts, int rank, int world, int epoch,
                          rf_stream_t stream) {
     if (!sync_all) return RF_ERR_NULL_POINTER;
@@ -93,8 +103,7 @@ int rf_moe_ep_dispatch(const void* x, const int* permuted_experts, const int* pe
 int rf_moe_ep_combine(void* const* y_all, const void* shared_fc2_output, const int* rev_permuted_rows,
                       const void* expanded_seq_softmax, const int* pair_rank, const int* pair_row, int n_tokens,
                       int top_k, int d_hidden, int world, void* final_output, rf_stream_t stream) {
-    if (!y_all || !shared_fc2_output || !rev_permuted_rows || !expanded_seq_softmax || !pair_rank || !pair_row ||
-        !final_output)
+    if (!y_all || !rev_permuted_rows || !expanded_seq_softmax || !pair_rank || !pair_row || !final_output)
         return RF_ERR_NULL_POINTER;
     if (world < 1 || world > 8 || top_k < 1 || top_k > 8 || d_hidden <= 0 || d_hidden % 8 != 0 || n_tokens < 0)
         return RF_ERR_BAD_SHAPE;

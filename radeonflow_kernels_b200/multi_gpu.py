@@ -266,8 +266,6 @@ class ExpertParallelMoE:
         self.ev_sent.record(self.side_stream)
         chk(L.rf_moe_grouped_gemm(x.data_ptr(), T, self._s_gate, self._s_up, self.single_offsets.data_ptr(), 1,
                                   self.fs, d, self.sh1.data_ptr(), s), "shared fc1")
-        chk(L.rf_moe_grouped_gemm(self.sh1.data_ptr(), T, self._s_down, None, self.single_offsets.data_ptr(), 1, d,
-                                  self.fs, self.sh2.data_ptr(), s), "shared fc2")
         main.wait_event(self.ev_sent)
         self._rendezvous(None, 0)                       # every rank's dispatch has landed
         chk(L.rf_moe_grouped_gemm(self.recv_x.local_ptr, self.capacity, self._w_gate, self._w_up,
@@ -275,9 +273,18 @@ class ExpertParallelMoE:
         chk(L.rf_moe_grouped_gemm(self.h.data_ptr(), self.capacity, self._w_down, None, self.recv_offsets.data_ptr(),
                                   self.E_loc, d, f, self.y.local_ptr, s), "routed fc2")
         self._rendezvous(None, 0)                       # every rank's expert outputs are complete
-        chk(L.rf_moe_ep_combine(self.y.ptr_array, self.sh2.data_ptr(), self.rev.data_ptr(), self.exp_w.data_ptr(),
+        # The combine pulls rows over NVLink on the side stream while the shared expert's second GEMM
+        # runs on the main stream; the shared rows are added afterwards.
+        self.ev_ready.record(main)
+        self.side_stream.wait_event(self.ev_ready)
+        chk(L.rf_moe_ep_combine(self.y.ptr_array, None, self.rev.data_ptr(), self.exp_w.data_ptr(),
                                 self.pair_rank.data_ptr(), self.pair_row.data_ptr(), T, K, d, self.world,
-                                self.out.data_ptr(), s), "rf_moe_ep_combine")
+                                self.out.data_ptr(), side), "rf_moe_ep_combine")
+        self.ev_sent.record(self.side_stream)
+        chk(L.rf_moe_grouped_gemm(self.sh1.data_ptr(), T, self._s_down, None, self.single_offsets.data_ptr(), 1, d,
+                                  self.fs, self.sh2.data_ptr(), s), "shared fc2")
+        main.wait_event(self.ev_sent)
+        chk(L.rf_moe_add_rows(self.out.data_ptr(), self.sh2.data_ptr(), T, d, s), "rf_moe_add_rows")
         return self.out
 
     def _rendezvous(self, counts_ptr, n_counts):
