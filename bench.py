@@ -302,6 +302,10 @@ def run_extras(args, rank, world, dev, dist, peaks):
     bias = torch.from_numpy(bias_np[order]).to(dev)
     layer = mg.ExpertParallelMoE(cfg, w, t_loc, dev, router_bias=bias)
     ms = _timed(lambda: layer.forward(x), 5, 2, dev, world, dist)
+    layer.trace = []
+    layer.forward(x)
+    stages = {name: round(ms_, 4) for name, ms_ in layer.stage_times_ms()}
+    layer.trace = None
     rows = torch.tensor([float(layer.received_rows())], dtype=torch.float64, device=dev)
     mx, sm = rows.clone(), rows.clone()
     if world > 1:
@@ -313,7 +317,7 @@ def run_extras(args, rank, world, dev, dist, peaks):
                   "per GPU by a static load-aware placement from one calibration pass; dispatch by peer stores, "
                   "combine by peer loads",
         "ms_per_layer": ms, "tokens_per_s": t_total / (ms * 1e-3), "tflops_total": fl / (ms * 1e-3) / 1e12,
-        "scaling": "strong", "rows_per_gpu_max": mx.item(), "rows_per_gpu_mean": sm.item() / world,
+        "stage_ms_rank0": stages, "scaling": "strong", "rows_per_gpu_max": mx.item(), "rows_per_gpu_mean": sm.item() / world,
         "imbalance_max_over_mean": mx.item() / (sm.item() / world)}
     layer.close()
     del layer, w, x

@@ -52,22 +52,31 @@ ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_
     }
 }
 
+// One row per block iteration: the row's indices are read once (not once per 16 bytes), then the
+// 256 threads move the row with up to four independent 16-byte loads in flight each before the
+// matching peer stores.
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted_experts,
                    const int* __restrict__ permuted_rows, const int* __restrict__ first_token_offset,
                    const int* __restrict__ send_base, int n_tokens, int n_pairs, int vec_per_row,
                    int experts_per_rank, PeerPtrs recv_x, int* __restrict__ pair_rank, int* __restrict__ pair_row) {
-    const size_t total = (size_t)n_pairs * vec_per_row;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int p = (int)(i / vec_per_row);
-        const int v = (int)(i - (size_t)p * vec_per_row);
-        const int e = permuted_experts[p];
+    for (int p = blockIdx.x; p < n_pairs; p += gridDim.x) {
+        const int e = __ldg(permuted_experts + p);
         const int q = e / experts_per_rank;
-        const int row = send_base[e] + (p - first_token_offset[e]);
-        const int tok = permuted_rows[p] % n_tokens;
-        uint4* dst = static_cast<uint4*>(pick_peer(recv_x, q)) + (size_t)row * vec_per_row + v;
-        *dst = __ldg(x + (size_t)tok * vec_per_row + v);
-        if (v == 0) {
+        const int row = __ldg(send_base + e) + (p - __ldg(first_token_offset + e));
+        const int tok = __ldg(permuted_rows + p) % n_tokens;
+        const uint4* src = x + (size_t)tok * vec_per_row;
+        uint4* dst = static_cast<uint4*>(pick_peer(recv_x, q)) + (size_t)row * vec_per_row;
+        for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += 4 * 256) {
+            uint4 r[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (v0 + j * 256 < vec_per_row) r[j] = __ldg(src + v0 + j * 256);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (v0 + j * 256 < vec_per_row) dst[v0 + j * 256] = r[j];
+        }
+        if (threadIdx.x == 0) {
             pair_rank[p] = q;
             pair_row[p] = row;
         }
@@ -207,11 +216,9 @@ cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, c
                                    int row_bytes, int experts_per_rank, const PeerPtrs& recv_x, int* pair_rank,
                                    int* pair_row, int num_sms, cudaStream_t stream) {
     const int vec = row_bytes / 16;
-    const size_t total = (size_t)n_pairs * vec;
-    if (total == 0) return cudaSuccess;
-    size_t blocks = (total + 255) / 256;
-    const size_t cap = (size_t)num_sms * 16;
-    if (blocks > cap) blocks = cap;
+    if (n_pairs == 0) return cudaSuccess;
+    int blocks = num_sms * 8;
+    if (blocks > n_pairs) blocks = n_pairs;
     ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(x), permuted_experts,
                                                              permuted_rows, first_token_offset, send_base, n_tokens,
                                                              n_pairs, vec, experts_per_rank, recv_x, pair_rank,

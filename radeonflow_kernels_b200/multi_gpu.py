@@ -182,6 +182,7 @@ class ExpertParallelMoE:
         self.capacity = int(capacity) if capacity else self.n_pairs * self.world
         self.weights = weights
         self.router_bias = router_bias
+        self.trace = None           # set to [] to time the stages of the next forward
         dev, T, K, E, d, f = self.device, self.T, self.K, self.E, self.d, self.f
         i32, f16 = torch.int32, torch.float16
         e = lambda shape, dt: torch.empty(shape, dtype=dt, device=dev)
@@ -237,6 +238,7 @@ class ExpertParallelMoE:
         T, K, E, d, f = self.T, self.K, self.E, self.d, self.f
         s = _stream()
         chk = _lib.check
+        self._mark("start")
         bias = self.router_bias.data_ptr() if self.router_bias is not None else None
         chk(L.rf_moe_router_gemm(x.data_ptr(), self.weights["router.weight"].data_ptr(), bias, T, E, d,
                                  self.scores.data_ptr(), s), "rf_moe_router_gemm")
@@ -250,6 +252,7 @@ class ExpertParallelMoE:
         # step after every rank's previous combine (its reads of our y buffer)
         torch.sub(self.first[1:], self.first[:-1], out=self.counts)
         self._rendezvous(self.counts.data_ptr(), E)
+        self._mark("route+counts")
         chk(L.rf_moe_ep_layout(self.counts_all.data_ptr(), self.rank, self.world, E, self.send_base.data_ptr(),
                                self.recv_offsets.data_ptr(), s), "rf_moe_ep_layout")
         # Dispatch runs on a side stream; the shared expert, which needs no exchange, runs on the main
@@ -266,26 +269,40 @@ class ExpertParallelMoE:
         self.ev_sent.record(self.side_stream)
         chk(L.rf_moe_grouped_gemm(x.data_ptr(), T, self._s_gate, self._s_up, self.single_offsets.data_ptr(), 1,
                                   self.fs, d, self.sh1.data_ptr(), s), "shared fc1")
-        main.wait_event(self.ev_sent)
-        self._rendezvous(None, 0)                       # every rank's dispatch has landed
-        chk(L.rf_moe_grouped_gemm(self.recv_x.local_ptr, self.capacity, self._w_gate, self._w_up,
-                                  self.recv_offsets.data_ptr(), self.E_loc, f, d, self.h.data_ptr(), s), "routed fc1")
-        chk(L.rf_moe_grouped_gemm(self.h.data_ptr(), self.capacity, self._w_down, None, self.recv_offsets.data_ptr(),
-                                  self.E_loc, d, f, self.y.local_ptr, s), "routed fc2")
-        self._rendezvous(None, 0)                       # every rank's expert outputs are complete
-        # The combine pulls rows over NVLink on the side stream while the shared expert's second GEMM
-        # runs on the main stream; the shared rows are added afterwards.
-        self.ev_ready.record(main)
-        self.side_stream.wait_event(self.ev_ready)
-        chk(L.rf_moe_ep_combine(self.y.ptr_array, None, self.rev.data_ptr(), self.exp_w.data_ptr(),
-                                self.pair_rank.data_ptr(), self.pair_row.data_ptr(), T, K, d, self.world,
-                                self.out.data_ptr(), side), "rf_moe_ep_combine")
-        self.ev_sent.record(self.side_stream)
         chk(L.rf_moe_grouped_gemm(self.sh1.data_ptr(), T, self._s_down, None, self.single_offsets.data_ptr(), 1, d,
                                   self.fs, self.sh2.data_ptr(), s), "shared fc2")
         main.wait_event(self.ev_sent)
-        chk(L.rf_moe_add_rows(self.out.data_ptr(), self.sh2.data_ptr(), T, d, s), "rf_moe_add_rows")
+        self._mark("dispatch+shared")
+        self._rendezvous(None, 0)                       # every rank's dispatch has landed
+        self._mark("barrier1")
+        chk(L.rf_moe_grouped_gemm(self.recv_x.local_ptr, self.capacity, self._w_gate, self._w_up,
+                                  self.recv_offsets.data_ptr(), self.E_loc, f, d, self.h.data_ptr(), s), "routed fc1")
+        self._mark("routed fc1")
+        chk(L.rf_moe_grouped_gemm(self.h.data_ptr(), self.capacity, self._w_down, None, self.recv_offsets.data_ptr(),
+                                  self.E_loc, d, f, self.y.local_ptr, s), "routed fc2")
+        self._mark("routed fc2")
+        self._rendezvous(None, 0)                       # every rank's expert outputs are complete
+        self._mark("barrier2")
+        # (Running the shared expert's second GEMM concurrently with this combine and adding its rows
+        # afterwards with rf_moe_add_rows was measured: no gain on 8 GPUs, and one more fp16 rounding.)
+        chk(L.rf_moe_ep_combine(self.y.ptr_array, self.sh2.data_ptr(), self.rev.data_ptr(), self.exp_w.data_ptr(),
+                                self.pair_rank.data_ptr(), self.pair_row.data_ptr(), T, K, d, self.world,
+                                self.out.data_ptr(), s), "rf_moe_ep_combine")
+        self._mark("combine")
         return self.out
+
+    def _mark(self, name):
+        """Stage timing aid: when `self.trace` is a list, records (name, CUDA event) pairs on the main stream."""
+        if self.trace is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream())
+            self.trace.append((name, ev))
+
+    def stage_times_ms(self):
+        """Milliseconds between consecutive marks of the last traced forward (synchronises)."""
+        torch.cuda.synchronize()
+        t = self.trace or []
+        return [(t[i][0], t[i - 1][1].elapsed_time(t[i][1])) for i in range(1, len(t))]
 
     def _rendezvous(self, counts_ptr, n_counts):
         self.epoch += 1
