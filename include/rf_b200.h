@@ -322,10 +322,11 @@ int rf_moe_ep_layout(const int *counts_all_dev, int rank, int world, int n_exper
 
 /* Dispatch: the token-row gather of expand_input (src/moe/moe_topk_kernel.cpp:174-213) writing
  * directly into the owner ranks' receive buffers `recv_x_all[r]` (fp16 [capacity, d_hidden]).
- * pair_rank / pair_row [n_pairs] record the destination of every locally sorted pair.         */
+ * pair_rank / pair_row [n_pairs] record the destination of every locally sorted pair.  Rank r
+ * sends to rank r+1 first, then r+2, ... so the senders never all target one GPU.         */
 int rf_moe_ep_dispatch(const void *x, const int *permuted_experts, const int *permuted_rows,
                        const int *first_token_offset, const int *send_base, int n_tokens, int n_pairs, int d_hidden,
-                       int n_experts, int world, void *const *recv_x_all, int *pair_rank, int *pair_row,
+                       int n_experts, int rank, int world, void *const *recv_x_all, int *pair_rank, int *pair_row,
                        rf_stream_t stream);
 
 /* Combine: reduce_output (src/moe/moe_topk_kernel.cpp:215-251) reading each expert output row

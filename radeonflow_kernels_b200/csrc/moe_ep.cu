@@ -59,8 +59,15 @@ __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted_experts,
                    const int* __restrict__ permuted_rows, const int* __restrict__ first_token_offset,
                    const int* __restrict__ send_base, int n_tokens, int n_pairs, int vec_per_row,
-                   int experts_per_rank, PeerPtrs recv_x, int* __restrict__ pair_rank, int* __restrict__ pair_row) {
-    for (int p = blockIdx.x; p < n_pairs; p += gridDim.x) {
+                   int experts_per_rank, int rank, int world, PeerPtrs recv_x, int* __restrict__ pair_rank,
+                   int* __restrict__ pair_row) {
+    // Pairs are sorted by expert, hence by destination rank.  Every source starts with a different
+    // destination (rank+1, rank+2, ...), so at any moment the senders target different GPUs instead of
+    // all writing into the same one.
+    const int p0 = __ldg(first_token_offset + ((rank + 1) % world) * experts_per_rank);
+    for (int i = blockIdx.x; i < n_pairs; i += gridDim.x) {
+        int p = i + p0;
+        if (p >= n_pairs) p -= n_pairs;
         const int e = __ldg(permuted_experts + p);
         const int q = e / experts_per_rank;
         const int row = __ldg(send_base + e) + (p - __ldg(first_token_offset + e));
@@ -213,16 +220,16 @@ cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int
 
 cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, const int* permuted_rows,
                                    const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs,
-                                   int row_bytes, int experts_per_rank, const PeerPtrs& recv_x, int* pair_rank,
-                                   int* pair_row, int num_sms, cudaStream_t stream) {
+                                   int row_bytes, int experts_per_rank, int rank, int world, const PeerPtrs& recv_x,
+                                   int* pair_rank, int* pair_row, int num_sms, cudaStream_t stream) {
     const int vec = row_bytes / 16;
     if (n_pairs == 0) return cudaSuccess;
     int blocks = num_sms * 8;
     if (blocks > n_pairs) blocks = n_pairs;
     ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(x), permuted_experts,
                                                              permuted_rows, first_token_offset, send_base, n_tokens,
-                                                             n_pairs, vec, experts_per_rank, recv_x, pair_rank,
-                                                             pair_row);
+                                                             n_pairs, vec, experts_per_rank, rank, world, recv_x,
+                                                             pair_rank, pair_row);
     return cudaGetLastError();
 }
 

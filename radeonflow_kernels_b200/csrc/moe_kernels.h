@@ -35,8 +35,8 @@ cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int
 // (peer stores) and records where it went (pair_rank, pair_row).
 cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, const int* permuted_rows,
                                    const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs,
-                                   int row_bytes, int experts_per_rank, const PeerPtrs& recv_x, int* pair_rank,
-                                   int* pair_row, int num_sms, cudaStream_t stream);
+                                   int row_bytes, int experts_per_rank, int rank, int world, const PeerPtrs& recv_x,
+                                   int* pair_rank, int* pair_row, int num_sms, cudaStream_t stream);
 // out[t] = fp16(sum_i w_i * Y_{rank_i}[row_i] + shared[t]) with Y rows read from the owner ranks (peer loads).
 cudaError_t moe_ep_combine_launch(const PeerPtrs& y, const void* shared_out, const int* rev, const void* weights,
                                   const int* pair_rank, const int* pair_row, int n_tokens, int top_k, int row_bytes,

@@ -263,7 +263,7 @@ class ExpertParallelMoE:
         self.side_stream.wait_event(self.ev_ready)
         side = ctypes.c_void_p(self.side_stream.cuda_stream)
         chk(L.rf_moe_ep_dispatch(x.data_ptr(), self.perm_experts.data_ptr(), self.perm_rows.data_ptr(),
-                                 self.first.data_ptr(), self.send_base.data_ptr(), T, T * K, d, E, self.world,
+                                 self.first.data_ptr(), self.send_base.data_ptr(), T, T * K, d, E, self.rank, self.world,
                                  self.recv_x.ptr_array, self.pair_rank.data_ptr(), self.pair_row.data_ptr(), side),
             "rf_moe_ep_dispatch")
         self.ev_sent.record(self.side_stream)
