@@ -417,8 +417,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                             } else {
                                 // N-split GEMM: the slab goes to every GPU's C (own memory and peers over
                                 // NVLink), which is the all-gather of C done by the epilogue itself
-                                for (int dd = 0; dd < p.n_dest; ++dd)
-                                    tma_store_2d(&dests.m[dd], slab, p.c_col_offset + col0 + ch * 64, slab_row0);
+                                // (own copy first, then rank+1, rank+2, ...: at any moment the ranks store
+                                // into different GPUs)
+                                for (int dd = 0; dd < p.n_dest; ++dd) {
+                                    int dst = p.dest_first + dd;
+                                    if (dst >= p.n_dest) dst -= p.n_dest;
+                                    tma_store_2d(&dests.m[dst], slab, p.c_col_offset + col0 + ch * 64, slab_row0);
+                                }
                             }
                             tma_store_commit();
                         }

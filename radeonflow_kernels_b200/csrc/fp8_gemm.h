@@ -20,6 +20,7 @@ struct GemmParams {
     long long as_row_stride, as_k_stride, bs_row_stride, bs_k_stride;
     int n_dest;             // copies of C to write (1, or the number of GPUs of an N-split GEMM)
     int c_col_offset;       // column of this GEMM's C inside each destination matrix
+    int dest_first;         // first destination to store to (N-split: own rank, so ranks target different GPUs)
 };
 
 // Output tensor maps of an N-split GEMM: entry d addresses GPU d's full row-major C.

@@ -127,6 +127,7 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
     p.bs_row_stride = k / 128; p.bs_k_stride = 1;
     p.n_dest = 1;
     p.c_col_offset = 0;
+    p.dest_first = 0;
     cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, nullptr, p, bn, sd->num_sms,
                                         reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {

@@ -175,6 +175,7 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     }
     p.n_dest = n_dest;
     p.c_col_offset = col_offset;
+    p.dest_first = (n_dest > 1 && dest_n > 0 && n > 0) ? (col_offset / n) % n_dest : 0;   // = rank for an N-split
     rf::GemmDestMaps dests;
     if (n_dest > 1) {
         for (int i = 0; i < 8; ++i) {
