@@ -542,12 +542,31 @@ def run_gpu_arm(args):
         h2d += sum(h[k2].numel() * h[k2].element_size() for k2 in ("a", "b", "as", "bs"))
         d2h += h["c"].numel() * 2
 
+    # Three streams, as a host application would drive `run`: operands go up on one stream, the GEMMs run
+    # on the second, results come back on the third; events chain shape i's copy-in -> GEMM -> copy-out,
+    # so PCIe traffic in both directions overlaps the compute of neighbouring shapes.
+    s_in = torch.cuda.Stream(device=dev)
+    s_out = torch.cuda.Stream(device=dev)
+    ev_in = [torch.cuda.Event() for _ in shapes]
+    ev_mm = [torch.cuda.Event() for _ in shapes]
+    ev_out = [torch.cuda.Event() for _ in shapes]
+
     def e2e_step():
-        for s, h in zip(shapes, host):
-            for k2 in ("a", "b", "as", "bs"):
-                s[k2].copy_(h[k2], non_blocking=True)
+        for i, (s, h) in enumerate(zip(shapes, host)):
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_mm[i])              # the previous step's GEMM has consumed the operands
+                for k2 in ("a", "b", "as", "bs"):
+                    s[k2].copy_(h[k2], non_blocking=True)
+                ev_in[i].record(s_in)
+            stream.wait_event(ev_in[i])
+            stream.wait_event(ev_out[i])               # the previous step's read-back of C is done
             launch(s)
-            h["c"].copy_(s["c"], non_blocking=True)
+            ev_mm[i].record(stream)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_mm[i])
+                h["c"].copy_(s["c"], non_blocking=True)
+                ev_out[i].record(s_out)
+        stream.wait_stream(s_out)                      # the step ends when its last result is on the host
 
     e2e_steps = max(1, min(args.steps, 5))
     e2e_step()

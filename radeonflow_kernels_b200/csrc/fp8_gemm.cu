@@ -75,9 +75,9 @@ struct GemmCfg {
     static constexpr int kSlabBytes = 32 * 128;               // per epilogue warp: 32 rows x 128 B, swizzled
     static constexpr int kSmemBytes =
         STAGES * kStageBytes + kEpiWarps * kSlabBytes + kBarBytes + 1024;       // + alignment slack
-    // 128 accumulators per thread need more than the 168 registers a 384-thread
-    // CTA starts with: the producer warpgroup gives registers to the epilogue.
-    static constexpr bool kRebalanceRegs = kColsPerThread > 64;
+    // The epilogue (64 or 128 accumulators per thread plus staging) wants more than the 168 registers a
+    // 384-thread CTA starts with, the producer warpgroup far fewer: registers are rebalanced.
+    static constexpr bool kRebalanceRegs = true;
     static_assert(kColsPerThread == 64 || kColsPerThread == 128, "epilogue handles 64 or 128 columns per thread");
     static_assert(kTmemCols == 512, "TMEM columns: power of two, at most 512");
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");

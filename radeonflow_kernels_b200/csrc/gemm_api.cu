@@ -51,7 +51,9 @@ GemmPlan plan_for(int m, int n, int k, int num_sms, int bn, int forced_split) {
     const int tiles = ((m + tr - 1) / tr) * ((n + tc - 1) / tc);
     const int kb = k / kBlockK;
     if (bn == 512) num_sms /= 2;     // work items go to CTA pairs
-    const double tile_w = bn == 512 ? 2.3 : bn / 128.0;   // relative time of one K block of one work item
+    // relative time of one K block of one work item, from in-kernel cycle counts
+    // (128 x 128: ~620 cycles, 128 x 256: ~790, CTA pair 256 x 256: ~925)
+    const double tile_w = bn == 512 ? 1.5 : (bn == 256 ? 1.25 : 1.0);
     GemmPlan best{bn, 1, 1e30};
     for (int s = 1; s <= 8; ++s) {
         if (forced_split > 0 && s != forced_split) continue;

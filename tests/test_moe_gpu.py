@@ -245,3 +245,39 @@ def test_full_size_layer_spot_checked():
         acc = sh2[j] + (sm[pos][:, None] * y_all[pos].cpu().numpy().astype(np.float32)).sum(axis=0)
         ok, nbad, mx = o.check(out[0, tok].cpu().numpy(), acc.astype(np.float16), RTOL, ATOL)
         assert ok, ("combine", tok, nbad, mx)
+
+
+def test_combine_without_shared_then_add_rows(rf_lib):
+    """`rf_moe_ep_combine` with the shared rows left out, followed by `rf_moe_add_rows`, equals the
+    one-pass combine up to the extra fp16 rounding (single-rank peer table: the local buffer)."""
+    t, k, d = 300, 4, 512
+    rng = np.random.default_rng(5)
+    y = rng.standard_normal((t * k, d)).astype(np.float16)
+    sh = rng.standard_normal((t, d)).astype(np.float16)
+    w = rng.random(t * k).astype(np.float16)
+    perm = rng.permutation(t * k).astype(np.int32)           # rev_permuted_rows: (i*T + t) -> position
+    dy, dsh, dw, drev = (torch.from_numpy(a).to(DEV) for a in (y, sh, w, perm))
+    rank = torch.zeros(t * k, dtype=torch.int32, device=DEV)
+    row = torch.arange(t * k, dtype=torch.int32, device=DEV)
+    out1 = torch.empty((t, d), dtype=torch.float16, device=DEV)
+    out2 = torch.empty((t, d), dtype=torch.float16, device=DEV)
+    ptrs = (ctypes.c_void_p * 1)(dy.data_ptr())
+    assert rf_lib.rf_moe_ep_combine(ptrs, dsh.data_ptr(), drev.data_ptr(), dw.data_ptr(), rank.data_ptr(),
+                                    row.data_ptr(), t, k, d, 1, out1.data_ptr(), None) == 0
+    assert rf_lib.rf_moe_ep_combine(ptrs, None, drev.data_ptr(), dw.data_ptr(), rank.data_ptr(), row.data_ptr(),
+                                    t, k, d, 1, out2.data_ptr(), None) == 0
+    assert rf_lib.rf_moe_add_rows(out2.data_ptr(), dsh.data_ptr(), t, d, None) == 0
+    torch.cuda.synchronize()
+    pos = perm.reshape(k, t)                                   # pos[i, t]
+    ref = sh.astype(np.float32) + sum(w[pos[i]].astype(np.float32)[:, None] * y[pos[i]].astype(np.float32)
+                                      for i in range(k))
+    ok, nbad, mx = o.check(out1.cpu().numpy(), ref.astype(np.float16), 2e-3, 2e-3)
+    assert ok, (nbad, mx)
+    ok, nbad, mx = o.check(out2.cpu().numpy(), ref.astype(np.float16), 4e-3, 4e-3)
+    assert ok, (nbad, mx)
+    # the local (single-GPU) combine entry gives the same result as the peer-table one
+    out3 = torch.empty((t, d), dtype=torch.float16, device=DEV)
+    assert rf_lib.rf_moe_combine(dy.data_ptr(), dsh.data_ptr(), drev.data_ptr(), dw.data_ptr(), t, k, d,
+                                 out3.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out1, out3)
