@@ -89,6 +89,16 @@ int rf_fp8_gemm_choose_split(int m, int n, int k);
 int rf_fp8_gemm_colmajor(const void *a, const void *b, const float *as, const float *bs, void *c, int m, int n,
                          int k, void *workspace, size_t workspace_bytes, rf_stream_t stream);
 
+/* rf_fp8_gemm_colmajor for operands whose bytes are e4m3fnuz (bias 8, the MI300X format the reference
+ * computes in: __hip_fp8_e4m3_fnuz, src/gemm/gemm_kernel.cpp:30-34; tests/checker/checker.cpp casts to
+ * torch.float8_e4m3fnuz).  A fnuz byte read as OCP e4m3fn is exactly twice its value, subnormals included,
+ * so the tensor cores consume the bytes unchanged and the epilogue multiplies the fp32 tile by 1/4 (exact).
+ * Three fnuz bytes have no counterpart under that reading: 0x80 (NaN), 0x7F and 0xFF (+-240).  Both
+ * operands are scanned on the stream before the GEMM; if one is found the GEMM still runs, and the next
+ * rf_device_status() returns RF_ERR_DEVICE_TIMEOUT with detail 16.  m*k and n*k must be multiples of 16. */
+int rf_fp8_gemm_colmajor_fnuz(const void *a, const void *b, const float *as, const float *bs, void *c, int m,
+                              int n, int k, void *workspace, size_t workspace_bytes, rf_stream_t stream);
+
 /* Allocation-free variant of rf_fp8_gemm.  It has no counterpart in the reference (whose `run`
  * allocates its scratch lazily with hipMalloc, src/gemm/gemm_launcher.cpp:30-36).
  *

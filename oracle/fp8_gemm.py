@@ -10,7 +10,7 @@ rounding.
 
 Layouts are the K-major ones: A [M,K] bytes, B [N,K] bytes, a_scale [M,K/128],
 b_scale [ceil(N/128),K/128], all row-major; C [M,N] bf16 returned as uint16 bits.
-FP8 bytes are OCP e4m3fn.
+FP8 bytes are OCP e4m3fn; the ``*_fnuz`` functions restate the same arithmetic for e4m3fnuz bytes.
 """
 import numpy as np
 
@@ -57,6 +57,72 @@ def encode_e4m3fn(x: np.ndarray) -> np.ndarray:
     code = np.where(pick_lo, lo, hi).astype(np.uint8)
     sign = (np.signbit(x)).astype(np.uint8) << 7
     return (code | sign).astype(np.uint8)
+
+
+def _e4m3fnuz_table() -> np.ndarray:
+    """e4m3fnuz (bias 8, no infinities, no negative zero; 0x80 is the one NaN): the format the
+    reference's kernels compute in (__hip_fp8_e4m3_fnuz, src/gemm/gemm_kernel.cpp:30-34) and its
+    checker casts to (torch.float8_e4m3fnuz, tests/checker/checker.cpp)."""
+    t = np.zeros(256, dtype=np.float32)
+    for b in range(256):
+        s = -1.0 if b & 0x80 else 1.0
+        e = (b >> 3) & 0xF
+        m = b & 0x7
+        if b == 0x80:
+            v = np.nan
+        elif e == 0:
+            v = s * (m / 8.0) * 2.0 ** (-7)
+        else:
+            v = s * (1.0 + m / 8.0) * 2.0 ** (e - 8)
+        t[b] = v
+    return t
+
+
+E4M3FNUZ_TO_F32 = _e4m3fnuz_table()
+
+
+def decode_e4m3fnuz(u8: np.ndarray) -> np.ndarray:
+    """Bytes (e4m3fnuz) -> fp32 values."""
+    return E4M3FNUZ_TO_F32[np.asarray(u8, dtype=np.uint8)]
+
+
+def encode_e4m3fnuz(x: np.ndarray) -> np.ndarray:
+    """fp32 -> nearest e4m3fnuz byte (ties to even mantissa), saturating at +-240; zero is always 0x00."""
+    x = np.asarray(x, dtype=np.float32)
+    pos = E4M3FNUZ_TO_F32[:0x80].astype(np.float64)         # 0 .. 240, ascending
+    ax = np.minimum(np.abs(x).astype(np.float64), 240.0)
+    hi = np.searchsorted(pos, ax, side="left").clip(0, len(pos) - 1)
+    lo = (hi - 1).clip(0, len(pos) - 1)
+    dlo = np.abs(ax - pos[lo])
+    dhi = np.abs(pos[hi] - ax)
+    pick_lo = (dlo < dhi) | ((dlo == dhi) & ((lo & 1) == 0))
+    code = np.where(pick_lo, lo, hi).astype(np.uint8)
+    sign = np.where(code == 0, 0, np.signbit(x).astype(np.uint8) << 7).astype(np.uint8)
+    return (code | sign).astype(np.uint8)
+
+
+def fp8_gemm_fnuz(a_u8, b_u8, a_scale, b_scale) -> np.ndarray:
+    """reference.py:40-85 on e4m3fnuz bytes - bf16 bits [M,N]."""
+    m, k = a_u8.shape
+    n = b_u8.shape[0]
+    a = decode_e4m3fnuz(a_u8) * np.repeat(a_scale.astype(np.float32), BLOCK, axis=1)[:, :k]
+    bs = np.repeat(np.repeat(b_scale.astype(np.float32), BLOCK, axis=0), BLOCK, axis=1)[:n, :k]
+    b = decode_e4m3fnuz(b_u8) * bs
+    return f32_to_bf16_bits(a @ b.T)
+
+
+def generate_input_fnuz(m: int, n: int, k: int, seed: int, amax: float = 224.0):
+    """Seeded e4m3fnuz operands: N(0,1) values (as the reference draws them, reference.py:28-31) stretched
+    so that part of them reaches the top binade, clipped to +-amax, rounded to e4m3fnuz; signed N(0,1)
+    scales.  amax < 232 keeps every byte inside the subset that reads as a finite e4m3fn value."""
+    rng = np.random.default_rng(seed)
+    a = encode_e4m3fnuz(np.clip(60.0 * rng.standard_normal((m, k), dtype=np.float32), -amax, amax))
+    b = encode_e4m3fnuz(np.clip(60.0 * rng.standard_normal((n, k), dtype=np.float32), -amax, amax))
+    kb = (k + BLOCK - 1) // BLOCK
+    nb = (n + BLOCK - 1) // BLOCK
+    a_s = (rng.standard_normal((m, kb), dtype=np.float32) / np.float32(60.0)).astype(np.float32)
+    b_s = (rng.standard_normal((nb, kb), dtype=np.float32) / np.float32(60.0)).astype(np.float32)
+    return a, b, a_s, b_s
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:

@@ -92,6 +92,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_fp8_gemm_choose_split.argtypes = [ci, ci, ci]
     L.rf_fp8_gemm_colmajor.restype = ci
     L.rf_fp8_gemm_colmajor.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp, sz, vp]
+    L.rf_fp8_gemm_colmajor_fnuz.restype = ci
+    L.rf_fp8_gemm_colmajor_fnuz.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp, sz, vp]
     L.rf_fp8_gemm_static_scratch.restype = ci
     L.rf_fp8_gemm_static_scratch.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
     # ---- MoE

@@ -342,7 +342,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             }
 #pragma unroll 4
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                const float s = qa[0] * qb[0];
+                // out_scale (reference-layout configurations only): 1, or 1/4 when the bytes are e4m3fnuz,
+                // which read as e4m3fn are twice their value in each operand.  A power of two commutes
+                // exactly with every rounding of the fp32 accumulation.
+                const float s = Cfg::kMnMajor ? qa[0] * qb[0] * p.out_scale : qa[0] * qb[0];
 #pragma unroll
                 for (int d = 0; d + 1 < PF; ++d) { qa[d] = qa[d + 1]; qb[d] = qb[d + 1]; }
                 {
@@ -388,7 +391,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 }
             }
             if (!ok) break;
-
             // Tile store: each warp stages its 32 rows x 128 bytes in its own swizzled
             // shared-memory slab and one lane hands the slab to the TMA, which writes
             // full 128-byte row segments and clips rows >= m / columns >= n.
@@ -488,6 +490,29 @@ splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restric
     *reinterpret_cast<uint2*>(c + i) = q;
 }
 
+// Flags e4m3fnuz bytes that have no e4m3fn counterpart when read as twice their value: 0x80 (NaN in
+// fnuz, -0 in fn) and 0x7F / 0xFF (+-240 in fnuz, NaN in fn).  Sets *status to kErrFnuzByte.
+__global__ void __launch_bounds__(256)
+fnuz_check_kernel(const uint4* __restrict__ bytes, size_t n_vec, int* status) {
+    bool bad = false;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 q = __ldg(bytes + i);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t x = w[j];
+            const uint32_t m7f = x & 0x7F7F7F7Fu;
+            // a byte equals 0x7F in its low 7 bits  <=>  (m7f + 0x01010101) has bit 7 set in that byte
+            const uint32_t is7f = (m7f + 0x01010101u) & 0x80808080u;
+            // a byte equals 0x80  <=>  low 7 bits zero and bit 7 set
+            const uint32_t low_zero = ~((m7f + 0x7F7F7F7Fu) | 0x7F7F7F7Fu);   // bit 7 set where low 7 bits == 0
+            const uint32_t is80 = low_zero & x & 0x80808080u;
+            bad |= (is7f | is80) != 0;
+        }
+    }
+    if (bad) atomicCAS(status, 0, (int)kErrFnuzByte);
+}
+
 using Cfg128 = GemmCfg<128, 6>;
 using Cfg256 = GemmCfg<256, 4>;
 using CfgPair = GemmCfg<256, 6, true>;      // 256 x 256 tile per CTA pair
@@ -542,6 +567,16 @@ extern "C" void rf_debug_wait_stats(unsigned long long* out8, int reset) {
     }
 }
 #endif
+
+cudaError_t fp8_fnuz_check_launch(const void* bytes, size_t n_bytes, int* status, int num_sms,
+                                  cudaStream_t stream) {
+    const size_t n_vec = n_bytes / 16;
+    if (n_vec == 0) return cudaSuccess;
+    size_t blocks = (n_vec + 255) / 256;
+    if (blocks > (size_t)num_sms * 8) blocks = (size_t)num_sms * 8;
+    fnuz_check_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(bytes), n_vec, status);
+    return cudaGetLastError();
+}
 
 cudaError_t fp8_gemm_prepare_device() {
     cudaError_t e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg128>, cudaFuncAttributeMaxDynamicSharedMemorySize,

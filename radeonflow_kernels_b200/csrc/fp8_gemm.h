@@ -20,6 +20,7 @@ struct GemmParams {
     long long as_row_stride, as_k_stride, bs_row_stride, bs_k_stride;
     int n_dest;             // copies of C to write (1, or the number of GPUs of an N-split GEMM)
     int c_col_offset;       // column of this GEMM's C inside each destination matrix
+    float out_scale;        // power-of-two factor applied once to the accumulated tile (1, or 1/4 for fnuz bytes)
     int dest_first;         // first destination to store to (N-split: own rank, so ranks target different GPUs)
 };
 
@@ -44,6 +45,10 @@ inline int gemm_b_box_rows(int block_n) { return block_n == 512 ? 128 : block_n;
 cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
                             const CUtensorMap& tma_p, const GemmDestMaps* dests, const GemmParams& p, int block_n,
                             int num_sms, cudaStream_t stream, bool mn_major = false);
+
+// Scans `n_bytes` (multiple of 16) of e4m3fnuz data for bytes that cannot be reinterpreted (0x80, 0x7F,
+// 0xFF); records kErrFnuzByte in *status if one is found.
+cudaError_t fp8_fnuz_check_launch(const void* bytes, size_t n_bytes, int* status, int num_sms, cudaStream_t stream);
 
 // Sets the launch attributes of every GEMM kernel configuration on the current device (normally done
 // lazily by the first launch of each configuration).

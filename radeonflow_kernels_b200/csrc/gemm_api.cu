@@ -92,7 +92,7 @@ GemmPlan choose_plan(int m, int n, int k, int num_sms, int forced_split) {
 int gemm_impl(const void* a, const void* b, const float* as, const float* bs, void* c, int m, int n, int k,
               int split_k, void* workspace, size_t workspace_bytes, bool own_workspace, cudaStream_t stream,
               void* const* dest_c = nullptr, int n_dest = 1, int dest_n = 0, int col_offset = 0,
-              bool mn_major = false) {
+              bool mn_major = false, bool fnuz = false) {
     if (!shape_ok(m, n, k)) return RF_ERR_BAD_SHAPE;
     if (mn_major && (m % 16) != 0) return RF_ERR_BAD_SHAPE;     // [k][m] rows must be 16-byte multiples for TMA
     if (n_dest > 1) {
@@ -177,6 +177,13 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     }
     p.n_dest = n_dest;
     p.c_col_offset = col_offset;
+    p.out_scale = fnuz ? 0.25f : 1.0f;
+    if (fnuz) {
+        if (((size_t)m * k) % 16 != 0 || ((size_t)n * k) % 16 != 0) return RF_ERR_BAD_SHAPE;
+        if (rf::fp8_fnuz_check_launch(a, (size_t)m * k, st->status, st->num_sms, stream) != cudaSuccess ||
+            rf::fp8_fnuz_check_launch(b, (size_t)n * k, st->status, st->num_sms, stream) != cudaSuccess)
+            return RF_ERR_CUDA;
+    }
     p.dest_first = (n_dest > 1 && dest_n > 0 && n > 0) ? (col_offset / n) % n_dest : 0;   // = rank for an N-split
     rf::GemmDestMaps dests;
     if (n_dest > 1) {
@@ -264,6 +271,12 @@ int rf_fp8_gemm_colmajor(const void* a, const void* b, const float* as, const fl
                          int k, void* workspace, size_t workspace_bytes, rf_stream_t stream) {
     return gemm_impl(a, b, as, bs, c, m, n, k, 0, workspace, workspace_bytes, workspace == nullptr,
                      reinterpret_cast<cudaStream_t>(stream), nullptr, 1, 0, 0, true);
+}
+
+int rf_fp8_gemm_colmajor_fnuz(const void* a, const void* b, const float* as, const float* bs, void* c, int m, int n,
+                              int k, void* workspace, size_t workspace_bytes, rf_stream_t stream) {
+    return gemm_impl(a, b, as, bs, c, m, n, k, 0, workspace, workspace_bytes, workspace == nullptr,
+                     reinterpret_cast<cudaStream_t>(stream), nullptr, 1, 0, 0, true, true);
 }
 
 void run(void* a, void* b, void* as, void* bs, void* c, int m, int n, int k, PerfMetrics* metrics,

@@ -26,6 +26,7 @@ enum DeviceError : int {
     kErrEpilogueWait = 4,   // epilogue timed out waiting for an accumulator
     kErrSchedWait = 5,      // tile-list / inter-CTA flag wait timed out
     kErrStoreWait = 6,      // epilogue timed out waiting for a staging buffer
+    kErrFnuzByte = 16,      // an e4m3fnuz input byte has no e4m3fn counterpart (0x80, 0x7F, 0xFF)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

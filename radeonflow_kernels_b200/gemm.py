@@ -60,9 +60,52 @@ def fp8_mm(a, b, a_scale, b_scale, c, split_k: int = 0, workspace=None):
     return c
 
 
+def fp8_mm_reference_layout(a, b, a_scale, b_scale, c, fnuz=None):
+    """The same product on the tensors the reference's generator hands out
+    (scripts/problems/gemm/reference.py:28-37): `a` is the transposed view of a contiguous [k, m] tensor,
+    `b` of [k, n], `a_scale` of [k/128, m], `b_scale` of [k/128, ceil(n/128)]; c is contiguous [m, n] bf16.
+    No transposed copy is made: the library reads the operands in place as MN-major tiles.
+
+    ``fnuz``: whether the bytes are e4m3fnuz (the reference's dtype); None = decide from the dtype, with
+    uint8 read as e4m3fn.  An e4m3fnuz operand must not hold NaN (0x80) or +-240 (0x7F / 0xFF);
+    `device_status()` reports 16 after a call that met one.
+    """
+    if not all(t.is_cuda for t in (a, b, a_scale, b_scale, c)):
+        raise ValueError("fp8_mm_reference_layout: all tensors must be CUDA tensors (there is no CPU path)")
+    for name, t in (("a", a), ("b", b), ("a_scale", a_scale), ("b_scale", b_scale)):
+        if t.dim() != 2 or not t.t().is_contiguous():
+            raise ValueError(f"fp8_mm_reference_layout: {name} must be the transpose of a contiguous tensor")
+    if not c.is_contiguous() or c.dtype != torch.bfloat16:
+        raise ValueError("fp8_mm_reference_layout: c must be contiguous bfloat16")
+    if a.element_size() != 1 or b.element_size() != 1:
+        raise ValueError("fp8_mm_reference_layout: a and b must be 1-byte e4m3 tensors")
+    if a_scale.dtype != torch.float32 or b_scale.dtype != torch.float32:
+        raise ValueError("fp8_mm_reference_layout: scales must be float32")
+    m, k = a.shape
+    n, k2 = b.shape
+    if k != k2 or tuple(c.shape) != (m, n):
+        raise ValueError("fp8_mm_reference_layout: shape mismatch")
+    if tuple(a_scale.shape) != (m, k // 128) or tuple(b_scale.shape) != ((n + 127) // 128, k // 128):
+        raise ValueError("fp8_mm_reference_layout: scale shape mismatch")
+    if fnuz is None:
+        fnuz = a.dtype == torch.float8_e4m3fnuz
+        if (b.dtype == torch.float8_e4m3fnuz) != fnuz:
+            raise ValueError("fp8_mm_reference_layout: a and b must use the same FP8 format")
+    L = _lib.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    entry = L.rf_fp8_gemm_colmajor_fnuz if fnuz else L.rf_fp8_gemm_colmajor
+    st = entry(a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), c.data_ptr(), m, n, k, None, 0,
+               stream)
+    _lib.check(st, entry.__name__)
+    return c
+
+
 def custom_kernel(data):
-    """scripts/gen_submission.py:327-330."""
+    """scripts/gen_submission.py:327-330.  Accepts both the K-major contiguous operands of `fp8_mm` and the
+    reference generator's own tuple (transposed views, e4m3fnuz), told apart by the strides of `a`."""
     a, b, a_scale, b_scale, c = data
+    if a.dim() == 2 and not a.is_contiguous() and a.t().is_contiguous():
+        return fp8_mm_reference_layout(a, b, a_scale, b_scale, c)
     fp8_mm(a, b, a_scale, b_scale, c)
     return c
 

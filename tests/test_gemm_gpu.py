@@ -215,3 +215,57 @@ def test_reference_physical_layout_rejects_unaligned_m(rf_lib):
                                      to_dev(a_s.T.copy()).data_ptr(), to_dev(b_s.T.copy()).data_ptr(), c.data_ptr(),
                                      72, 64, 128, None, 0, None)
     assert st == 1
+
+
+@pytest.mark.parametrize("m,n,k,seed", [(64, 64, 128, 21), (96, 576, 512, 22), (1024, 1536, 7168, 23),
+                                         (6144, 512, 1024, 24), (1040, 320, 1024, 25)])
+def test_fnuz_entry_matches_fnuz_oracle(rf_lib, m, n, k, seed):
+    """`rf_fp8_gemm_colmajor_fnuz`: reference layout and the reference's FP8 format (e4m3fnuz bytes)."""
+    a, b, a_s, b_s = o.generate_input_fnuz(m, n, k, seed)
+    from tests.helpers import to_dev
+    da, db = to_dev(np.ascontiguousarray(a.T)), to_dev(np.ascontiguousarray(b.T))
+    das, dbs = to_dev(np.ascontiguousarray(a_s.T)), to_dev(np.ascontiguousarray(b_s.T))
+    full, c = canary_output(m, n)
+    st = rf_lib.rf_fp8_gemm_colmajor_fnuz(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(),
+                                          c.data_ptr(), m, n, k, None, 0, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    assert canary_intact(full, m, n)
+    assert_close(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm_fnuz(a, b, a_s, b_s))
+
+
+def test_custom_kernel_takes_the_reference_generators_tuple():
+    """Tensors built the way scripts/problems/gemm/reference.py:28-37 builds them (randn cast to
+    float8_e4m3fnuz in [k, m] / [k, n], scales [k/128, m] / [k/128, n/128], all handed over as .T views)
+    go through `custom_kernel` unchanged."""
+    m, n, k = 1024, 576, 1024
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(77)
+    a = torch.randn((k, m), dtype=torch.bfloat16, device="cuda", generator=gen).to(torch.float8_e4m3fnuz)
+    b = torch.randn((k, n), dtype=torch.bfloat16, device="cuda", generator=gen).to(torch.float8_e4m3fnuz)
+    a_s = torch.randn((k // 128, m), dtype=torch.float32, device="cuda", generator=gen)
+    b_s = torch.randn((k // 128, (n + 127) // 128), dtype=torch.float32, device="cuda", generator=gen)
+    c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    out = G.custom_kernel((a.T, b.T, a_s.T, b_s.T, c))
+    torch.cuda.synchronize()
+    assert out is c and G.device_status() == 0
+    exp = o.fp8_gemm_fnuz(a.T.contiguous().view(torch.uint8).cpu().numpy(), b.T.contiguous().view(torch.uint8).cpu().numpy(),
+                          a_s.T.contiguous().cpu().numpy(), b_s.T.contiguous().cpu().numpy())
+    assert_close(c.view(torch.uint16).cpu().numpy(), exp)
+
+
+@pytest.mark.parametrize("bad,where", [(0x80, "a"), (0x7F, "b"), (0xFF, "a")])
+def test_fnuz_entry_reports_bytes_it_cannot_read(rf_lib, bad, where):
+    m, n, k = 64, 128, 256
+    a, b, a_s, b_s = o.generate_input_fnuz(m, n, k, 31)
+    (a if where == "a" else b)[5, 77] = bad
+    from tests.helpers import to_dev
+    da, db = to_dev(np.ascontiguousarray(a.T)), to_dev(np.ascontiguousarray(b.T))
+    das, dbs = to_dev(np.ascontiguousarray(a_s.T)), to_dev(np.ascontiguousarray(b_s.T))
+    c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda:0")
+    st = rf_lib.rf_fp8_gemm_colmajor_fnuz(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(),
+                                          c.data_ptr(), m, n, k, None, 0, None)
+    assert st == 0
+    assert G.device_status() == 16          # recorded, and cleared by the read
+    assert G.device_status() == 0

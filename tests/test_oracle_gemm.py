@@ -72,3 +72,36 @@ def test_generator_is_seeded_and_clipped():
     assert np.nanmax(np.abs(o.decode_e4m3fn(a))) <= 240
     assert a_s.shape == (64, 2) and b_s.shape == (1, 2)
     assert a_s.min() >= 0.5 * 2 ** -7 and a_s.max() <= 2.0 * 2 ** -7
+
+
+def test_e4m3fnuz_table_matches_torch():
+    """The oracle's e4m3fnuz decode is torch's float8_e4m3fnuz (the dtype the reference generator casts to,
+    scripts/problems/gemm/reference.py:28-29) for all 256 bytes, and its encoder rounds like torch's cast."""
+    import torch
+    t = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fnuz).float().numpy()
+    assert np.array_equal(np.isnan(t), np.isnan(o.E4M3FNUZ_TO_F32))
+    ok = ~np.isnan(t)
+    assert np.array_equal(t[ok], o.E4M3FNUZ_TO_F32[ok])
+    x = (np.random.default_rng(5).standard_normal(200000) * 70).astype(np.float32).clip(-240, 240)
+    x[:16] = [0.0, -0.0, 2.0 ** -10, -2.0 ** -10, 2.0 ** -11, 240, -240, 232, 1.0625, 1.1875, 3e-4, -3e-4, 0.5, 1, 2, 4]
+    mine = o.encode_e4m3fnuz(x)
+    theirs = torch.from_numpy(x).to(torch.float8_e4m3fnuz).view(torch.uint8).numpy()
+    assert np.array_equal(mine, theirs)
+
+
+def test_e4m3fnuz_byte_is_half_its_e4m3fn_reading():
+    """The identity the fnuz entry rests on: every e4m3fnuz byte except 0x80, 0x7F and 0xFF, read as
+    e4m3fn, is exactly twice its value (subnormals included)."""
+    for b in range(256):
+        if b in (0x80, 0x7F, 0xFF):
+            assert not np.isfinite(o.E4M3FN_TO_F32[b]) or b == 0x80
+            continue
+        assert o.E4M3FN_TO_F32[b] == 2.0 * o.E4M3FNUZ_TO_F32[b]
+
+
+def test_fnuz_oracle_is_quarter_of_fn_oracle_on_shared_bytes():
+    a, b, a_s, b_s = o.generate_input_fnuz(48, 128, 256, 11)
+    assert not np.isin(a, [0x80, 0x7F, 0xFF]).any() and not np.isin(b, [0x80, 0x7F, 0xFF]).any()
+    fz = o.bf16_bits_to_f32(o.fp8_gemm_fnuz(a, b, a_s, b_s))
+    fn = o.bf16_bits_to_f32(o.f32_to_bf16_bits(np.float32(0.25) * o.fp8_gemm_f32(a, b, a_s, b_s)))
+    assert np.allclose(fz, fn, rtol=2 ** -7, atol=1e-6 * np.abs(fz).max())
