@@ -25,6 +25,7 @@
 #include "fp8_gemm.h"
 
 #include <cstdio>
+#include <cstdlib>
 
 namespace rf {
 
@@ -132,6 +133,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     constexpr bool TWO = Cfg::kTwoCta;
+    // The next kernel in the stream may be scheduled onto SMs as this grid's CTAs leave them; it blocks in
+    // its own griddep_wait() until this grid has completed.
+    griddep_launch_dependents();
 #ifdef RF_SINGLE_ISSUE
     constexpr bool kDualIssue = false;
 #else
@@ -171,12 +175,24 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     if (TWO) cluster_sync_all();     // both CTAs' barriers exist before any remote arrive or multicast commit
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot_ptr);
+    // Barriers, TMEM and descriptors are set up; everything below reads or writes global memory that the
+    // previous kernel in the stream may still be producing.
+    griddep_wait();
 
     const int total_work = p.tiles_m * p.tiles_n * p.splits;
     const int kb_total = p.k / BK;
 
     if (warp < NUM_NON_EPI_WARPS) {
-    if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 120;\n");
+// Register split after set-up: 4 producer / MMA warps at RF_REGS_LO, 8 epilogue warps at RF_REGS_HI
+// (128 * LO + 256 * HI <= 64512, the CTA's allocation at 168 per thread).  Measured on the 18-shape sweep:
+// 120 / 192 is the fastest split; 104 / 200 is 5 % slower, 208 and above 1.5x slower.
+#ifndef RF_REGS_LO
+#define RF_REGS_LO 120
+#define RF_REGS_HI 192
+#endif
+#define RF_STR2(x) #x
+#define RF_STR(x) RF_STR2(x)
+    if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 " RF_STR(RF_REGS_LO) ";\n");
     // Producer and MMA warps keep all 32 lanes in the loops (warp-uniform control
     // flow, so descriptors and addresses live in uniform registers) and elect one
     // lane only for the instructions that must be issued once.
@@ -295,7 +311,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
     } else {
         // ---------------------------------------------------------- epilogue
-        if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 192;\n");
+        if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 " RF_STR(RF_REGS_HI) ";\n");
         const int ew = warp - NUM_NON_EPI_WARPS;
         const int quad = warp & 3;            // TMEM lane quadrant this warp may access
         const int grp = ew >> 2;              // column group
@@ -364,6 +380,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 if (ew == 0 && lane == 0) mbar_arrive(empty_bar(it % STAGES));
                 const uint32_t taddr = lane_addr + buf * BN + grp * CPT;
                 constexpr int NCH = CPT / 32;
+                auto release_buffer = [&] {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (TWO) mbar_arrive_cluster_relaxed(mapa_cluster(tmem_empty_bar(buf), 0));
+                        else mbar_arrive(tmem_empty_bar(buf));
+                    }
+                };
                 // Staging registers: two 32-column buffers (the load of chunk c+1 overlaps the FMAs of
                 // chunk c) when a thread owns 64 columns; one buffer when it owns 128, because 128
                 // accumulators leave no room for a second one (the other epilogue warp on the same
@@ -375,14 +399,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 for (int c = 0; c < NCH; ++c) {
                     tmem_ld_fence(v[c % NV]);   // waits for every load issued so far
                     if (NV == 2 && c + 1 < NCH) tmem_ld32_async(taddr + (c + 1) * 32, v[(c + 1) % NV]);
-                    if (c + 1 == NCH) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (TWO) mbar_arrive_cluster_relaxed(mapa_cluster(tmem_empty_bar(buf), 0));
-                            else mbar_arrive(tmem_empty_bar(buf));
-                        }
-                    }
+                    if (c + 1 == NCH) release_buffer();
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         acc[c * 16 + j] =
@@ -477,6 +494,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 // src/gemm/gemm_kernel.cpp:288-303).  One float4 per thread per slice.
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ c, size_t mn, int splits) {
+    griddep_launch_dependents();
+    griddep_wait();     // the slices come from the GEMM launched just before
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= mn) return;
     float4 acc = *reinterpret_cast<const float4*>(partial + i);
@@ -519,6 +538,16 @@ using CfgPair = GemmCfg<256, 6, true>;      // 256 x 256 tile per CTA pair
 using Cfg128Mn = GemmCfg<128, 6, false, true>;
 using Cfg256Mn = GemmCfg<256, 4, false, true>;
 
+// Programmatic dependent launch between consecutive GEMM-path kernels of a stream (the launch latency and
+// the barrier / TMEM set-up of kernel i+1 overlap the tail of kernel i).  RF_FP8_GEMM_PDL=0 switches it off.
+bool overlap_launches() {
+    static const bool on = [] {
+        const char* e = getenv("RF_FP8_GEMM_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 template <class Cfg>
 cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
                        const CUtensorMap& tma_p, const GemmDestMaps& dests, const GemmParams& p, int num_sms,
@@ -535,8 +564,17 @@ cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const
     const int total = p.tiles_m * p.tiles_n * p.splits;
     if (!Cfg::kTwoCta) {
         const int grid = total < num_sms ? total : num_sms;
-        kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tma_a, tma_b, tma_c, tma_p, dests, p);
-        return cudaGetLastError();
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid, 1, 1);
+        cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
+        cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = overlap_launches() ? 1 : 0;
+        return cudaLaunchKernelEx(&cfg, kernel, tma_a, tma_b, tma_c, tma_p, dests, p);
     }
     // CTA pairs: clusters of 2 along x, one pair per work item at most
     const int pairs = total < num_sms / 2 ? total : num_sms / 2;
@@ -614,8 +652,17 @@ cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, 
     if (p.splits > 1) {
         const size_t mn = (size_t)p.m * p.n;
         const unsigned blocks = (unsigned)((mn / 4 + 255) / 256);
-        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.partial, p.c, mn, p.splits);
-        e = cudaGetLastError();
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(blocks, 1, 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = overlap_launches() ? 1 : 0;
+        e = cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, (const float*)p.partial, (__nv_bfloat16*)p.c, mn,
+                               (int)p.splits);
     }
     return e;
 }

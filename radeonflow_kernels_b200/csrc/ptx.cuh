@@ -94,6 +94,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     }
 }
 
+// ----------------------------------------------- programmatic dependent launch --
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel
+// before it in the stream is still running.  griddep_wait() blocks until that kernel has completed and
+// its memory operations are visible; it must come before the first global access.  Without the launch
+// attribute both instructions are no-ops.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // --------------------------------------------------------------------- TMA --
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
