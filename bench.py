@@ -35,6 +35,11 @@ NK_PAIRS = [(1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), 
             (512, 7168), (4096, 512)]
 SWEEP = [(m, n, k) for m in (1024, 6144) for (n, k) in NK_PAIRS]
 CPU_SAMPLE = [(1024, n, k) for (n, k) in NK_PAIRS]      # the M=1024 half: ~190 GFLOP per pass
+# dram__bytes_read.sum + dram__bytes_write.sum of fp8_gemm_kernel for each sweep shape, in SWEEP order, from one
+# ncu pass over the first sweep of `bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-extras`
+# (profiles/fp8_gemm_kernel_sweep.md, section 3).  C mostly stays in the 126 MB L2, hence traffic < algorithmic.
+NCU_DRAM_BYTES = [18623744, 6396672, 11739904, 2159104, 16898048, 40659712, 19004416, 11280640, 2690816,
+                  56950272, 14554880, 49672704, 30538752, 60639232, 114914816, 65986304, 49144320, 5449984]
 METRIC = "fp8_blockscaled_gemm_tflops"
 UNIT = "TFLOP/s"
 
@@ -616,7 +621,10 @@ def run_gpu_arm(args):
                        "launch": "one CUDA graph replay per step",
                        "parallelism": "replicas" if world > 1 else "single"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
-                         "frac": achieved / fp8_peak, "traffic": None,
+                         "frac": achieved / fp8_peak,
+                         "traffic": (sum(NCU_DRAM_BYTES) / len(NCU_DRAM_BYTES) if not args.shapes else None),
+                         "traffic_note": "DRAM bytes per fp8_gemm_kernel launch, mean over the 18 shapes, ncu; "
+                                         f"algorithmic mean {sum(gemm_bytes(*x) for x in SWEEP) / len(SWEEP):.0f}",
                          "peak_source": f"2 x bf16_tflops of {peaks['source']} (fp8 rate = 2 x bf16)",
                          "kernel": "fp8_gemm_kernel"},
             "cpu_baseline": cpu,
