@@ -80,6 +80,7 @@ const CUtensorMap* weight_maps(const void* const* ptrs, int count, int rows, int
 struct Aux {
     int* tile_group;
     int* tile_row0;
+    int* tile_chunk;
     int* tile_count;
     int* single_offsets;   // [2] = {0, T} for the shared expert / router (one group)
     int* sort_scratch;
@@ -87,7 +88,7 @@ struct Aux {
 
 size_t aux_bytes(int n_rows_expanded, int n_experts) {
     const size_t max_tiles = (size_t)n_rows_expanded / 128 + n_experts + 2;
-    return align_up(max_tiles * 4, 256) * 2 + 256 + 256 +
+    return align_up(max_tiles * 4, 256) * 3 + 256 + 256 +
            align_up(rf::moe_permute_scratch_bytes(n_rows_expanded, n_experts), 256);
 }
 
@@ -98,6 +99,8 @@ bool carve_aux(Aux* a, int n_rows_expanded, int n_experts) {
     a->tile_group = reinterpret_cast<int*>(base);
     base += align_up(max_tiles * 4, 256);
     a->tile_row0 = reinterpret_cast<int*>(base);
+    base += align_up(max_tiles * 4, 256);
+    a->tile_chunk = reinterpret_cast<int*>(base);
     base += align_up(max_tiles * 4, 256);
     a->tile_count = reinterpret_cast<int*>(base);
     base += 256;
@@ -174,12 +177,13 @@ int grouped_gemm(int mode, const void* x, int n_rows, const void* const* w_host,
     } else {
         to = ta;
     }
-    if (rf::moe_tile_list_launch(offsets_dev, n_groups, aux.tile_group, aux.tile_row0, aux.tile_count, stream) !=
+    if (rf::moe_tile_list_launch(offsets_dev, n_groups, aux.tile_group, aux.tile_row0, aux.tile_chunk, aux.tile_count, stream) !=
         cudaSuccess)
         return RF_ERR_CUDA;
     rf::MoeGemmParams p;
     p.tile_group = aux.tile_group;
     p.tile_row0 = aux.tile_row0;
+    p.tile_chunk = aux.tile_chunk;
     p.tile_count = aux.tile_count;
     p.group_offsets = offsets_dev;
     p.b_maps = maps;

@@ -47,16 +47,16 @@ __device__ __forceinline__ float silu_fp16_rounded(float g) {
     return __half2float(__float2half_rn(s));
 }
 
-// Work item -> (row tile, column block).  Items walk 8 consecutive row tiles (about one expert's rows)
-// for one column block, then the next column block of the same 8 tiles: CTAs running at the same time
-// share the weight column block (read from HBM once per expert and chunk) while the 8 A tiles stay in
-// L2 across all column blocks.
-__device__ __forceinline__ void decode_item(int w, int n_tiles, int nbn, int* tile, int* nb) {
-    constexpr int GROUP = 8;
-    const int chunk = w / (GROUP * nbn);
-    const int first = chunk * GROUP;
-    const int rows = min(GROUP, n_tiles - first);
-    const int r = w - chunk * GROUP * nbn;
+// Work item -> (row tile, column block).  Items walk one chunk (up to kMoeChunkTiles row tiles of one
+// group, built by tile_list_kernel) for one column block, then the next column block of the same chunk:
+// the CTAs running at the same time share that group's weight column block, and the chunk's A tiles stay
+// in L2 across all column blocks.  The chunk of work item w is the chunk of tile w / nbn, because the
+// chunks before it hold exactly (first tile of the chunk) * nbn items.
+__device__ __forceinline__ void decode_item(int w, const int* __restrict__ tile_chunk, int nbn, int* tile, int* nb) {
+    const int info = __ldg(tile_chunk + w / nbn);
+    const int first = info >> 8;
+    const int rows = info & 0xff;
+    const int r = w - first * nbn;
     *nb = r / rows;
     *tile = first + r % rows;
 }
@@ -115,7 +115,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         bool ok = true;
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
             int tile, nb_i;
-            decode_item(w, n_tiles, nbn, &tile, &nb_i);
+            decode_item(w, p.tile_chunk, nbn, &tile, &nb_i);
             const int n0 = nb_i * TILE_N;
             const int row0 = __ldg(p.tile_row0 + tile);
             const int grp = __ldg(p.tile_group + tile);
@@ -195,7 +195,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         bool ok = true;
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tcount) {
             int tile, nb_i;
-            decode_item(w, n_tiles, nbn, &tile, &nb_i);
+            decode_item(w, p.tile_chunk, nbn, &tile, &nb_i);
             const int n0 = nb_i * TILE_N;
             const int row0 = __ldg(p.tile_row0 + tile);
             const int grp = __ldg(p.tile_group + tile);

@@ -19,8 +19,8 @@ cudaError_t moe_combine_launch(const void* y, const void* shared_out, const int*
                                int n_tokens, int top_k, int row_bytes, void* out, cudaStream_t stream);
 // dst[0] = a, dst[1] = b (a one-group offsets array written in stream order)
 cudaError_t moe_set_range_launch(int* dst, int a, int b, cudaStream_t stream);
-cudaError_t moe_tile_list_launch(const int* offsets, int n_groups, int* tile_group, int* tile_row0, int* tile_count,
-                                 cudaStream_t stream);
+cudaError_t moe_tile_list_launch(const int* offsets, int n_groups, int* tile_group, int* tile_row0, int* tile_chunk,
+                                 int* tile_count, cudaStream_t stream);
 
 // ---- expert-parallel exchange over peer memory (moe_ep.cu)
 struct PeerPtrs {
@@ -60,9 +60,13 @@ enum MoeGemmMode {
     kMoeGemmRouter = 2,   // out[r, n] = fp16(X[r,:] . W[n,:] + bias[n]); W is [N, K] row-major (K contiguous)
 };
 
+// Largest run of row tiles of one group that the grouped GEMM walks together (see tile_list_kernel).
+constexpr int kMoeChunkTiles = 16;
+
 struct MoeGemmParams {
     const int* tile_group;      // [n_tiles] group (expert) of each 128-row tile
     const int* tile_row0;       // [n_tiles] first row of the tile
+    const int* tile_chunk;      // [n_tiles] (first tile of the tile's chunk << 8) | tiles in the chunk
     const int* tile_count;      // [1]
     const int* group_offsets;   // [n_groups + 1] row range of each group
     const CUtensorMap* b_maps;  // device array, one tensor map per group (first weight)

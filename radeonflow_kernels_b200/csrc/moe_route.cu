@@ -289,9 +289,13 @@ combine_kernel(const uint4* __restrict__ y, const uint4* __restrict__ shared_out
 
 // Row ranges [offsets[g], offsets[g+1]) -> list of 128-row tiles: tile_group[i], tile_row0[i];
 // tile_count[0] = number of tiles.  One block; groups <= 1024.
+// tile_chunk[i] = (first tile of i's chunk << 8) | tiles in the chunk.  A chunk is a run of at most
+// kMoeChunkTiles consecutive tiles of ONE group (a group's tiles are split into equal chunks); the grouped
+// GEMM walks a chunk column block by column block, so the CTAs that run at the same time share one
+// group's weight column block and the chunk's row tiles.
 __global__ void __launch_bounds__(1024)
 tile_list_kernel(const int* __restrict__ offsets, int n_groups, int* __restrict__ tile_group,
-                 int* __restrict__ tile_row0, int* __restrict__ tile_count) {
+                 int* __restrict__ tile_row0, int* __restrict__ tile_chunk, int* __restrict__ tile_count) {
     __shared__ int warp_sums[32];
     const int g = threadIdx.x;
     const int lane = g & 31, warp = g >> 5;
@@ -319,9 +323,21 @@ tile_list_kernel(const int* __restrict__ offsets, int n_groups, int* __restrict_
     }
     __syncthreads();
     const int start = (warp > 0 ? warp_sums[warp - 1] : 0) + incl - n;
+    const int n_chunks = (n + kMoeChunkTiles - 1) / kMoeChunkTiles;
+    const int base = n_chunks ? n / n_chunks : 0;
+    const int rem = n_chunks ? n % n_chunks : 0;          // the first `rem` chunks hold base + 1 tiles
     for (int i = 0; i < n; ++i) {
         tile_group[start + i] = g;
         tile_row0[start + i] = lo + i * 128;
+        int c_first, c_size;
+        if (i < rem * (base + 1)) {
+            c_size = base + 1;
+            c_first = (i / c_size) * c_size;
+        } else {
+            c_size = base;
+            c_first = rem * (base + 1) + ((i - rem * (base + 1)) / base) * base;
+        }
+        tile_chunk[start + i] = ((start + c_first) << 8) | c_size;
     }
     if (g == 1023) tile_count[0] = start + n;
 }
@@ -399,9 +415,9 @@ cudaError_t moe_combine_launch(const void* y, const void* shared_out, const int*
     return cudaGetLastError();
 }
 
-cudaError_t moe_tile_list_launch(const int* offsets, int n_groups, int* tile_group, int* tile_row0, int* tile_count,
-                                 cudaStream_t stream) {
-    tile_list_kernel<<<1, 1024, 0, stream>>>(offsets, n_groups, tile_group, tile_row0, tile_count);
+cudaError_t moe_tile_list_launch(const int* offsets, int n_groups, int* tile_group, int* tile_row0, int* tile_chunk,
+                                 int* tile_count, cudaStream_t stream) {
+    tile_list_kernel<<<1, 1024, 0, stream>>>(offsets, n_groups, tile_group, tile_row0, tile_chunk, tile_count);
     return cudaGetLastError();
 }
 
