@@ -80,6 +80,20 @@ size_t rf_fp8_gemm_workspace_bytes(int m, int n, int k, int split_k);
  * device (reference: dispatch table, src/gemm/gemm_launcher.cpp:229-247).    */
 int rf_fp8_gemm_choose_split(int m, int n, int k);
 
+/* Tuned-plan table: (tile width, split-K) per exact shape, consulted before the cost model.  It replaces
+ * the reference's compile-time dispatch table and the offline tuner that regenerates it
+ * (src/gemm/gemm_launcher.cpp:229-247, tuner/gemm_tuner.py:343-385, tuner/gemm_batch.py:8-27).
+ * block_n: 128 or 256 (tile 128 x block_n), 512 = CTA pair (256 x 256); block_n == 0 removes the entry.
+ * The library starts with a built-in table for the benchmark shapes (RF_FP8_GEMM_NO_BUILTIN_PLANS=1 drops
+ * it) and reads the file named by RF_FP8_GEMM_PLANS at first use.                                       */
+int rf_fp8_gemm_set_plan(int m, int n, int k, int block_n, int split_k);
+/* The plan the library would use (table entry or cost model; 148 SMs assumed when no GPU is present).   */
+int rf_fp8_gemm_get_plan(int m, int n, int k, int *block_n, int *split_k);
+/* Text file, one "m n k block_n split_k" per line, '#' comments (what `python -m
+ * radeonflow_kernels_b200.tune` writes).  Returns the number of entries loaded, -1 if the file cannot be
+ * read, -2 if a line was malformed (the valid lines are still loaded).                                  */
+int rf_fp8_gemm_load_plans(const char *path);
+
 /* Same arithmetic with the operands in the reference's own physical layout
  * (src/gemm/gemm_kernel_legacy.cpp:264-268; scripts/problems/gemm/reference.py:28-37 creates (k,m) and
  * returns .T): a [k][m], b [k][n] (m / n contiguous), as [k/128][m], bs [k/128][ceil(n/128)], c [m][n].

@@ -90,6 +90,12 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_fp8_gemm_workspace_bytes.argtypes = [ci, ci, ci, ci]
     L.rf_fp8_gemm_choose_split.restype = ci
     L.rf_fp8_gemm_choose_split.argtypes = [ci, ci, ci]
+    L.rf_fp8_gemm_set_plan.restype = ci
+    L.rf_fp8_gemm_set_plan.argtypes = [ci, ci, ci, ci, ci]
+    L.rf_fp8_gemm_get_plan.restype = ci
+    L.rf_fp8_gemm_get_plan.argtypes = [ci, ci, ci, ctypes.POINTER(ci), ctypes.POINTER(ci)]
+    L.rf_fp8_gemm_load_plans.restype = ci
+    L.rf_fp8_gemm_load_plans.argtypes = [ctypes.c_char_p]
     L.rf_fp8_gemm_colmajor.restype = ci
     L.rf_fp8_gemm_colmajor.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp, sz, vp]
     L.rf_fp8_gemm_colmajor_fnuz.restype = ci

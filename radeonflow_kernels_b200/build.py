@@ -39,6 +39,7 @@ def _stale() -> bool:
         return True
     t = os.path.getmtime(LIB_PATH)
     deps = sources() + glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
+    deps += glob.glob(os.path.join(CSRC, "*.inc"))
     deps.append(os.path.join(os.path.dirname(PKG_DIR), "include", "rf_b200.h"))
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 

@@ -58,4 +58,7 @@ cudaError_t fp8_gemm_prepare_device();
 // `num_sms` SMs; `split_k` > 0 forces the slice count.
 void fp8_gemm_plan(int m, int n, int k, int num_sms, int split_k, int* block_n, int* splits);
 
+// Exact-shape entry of the tuned-plan table (built-in, registered or loaded from a file); false = none.
+bool tuned_plan_lookup(int m, int n, int k, int* block_n, int* splits);
+
 }  // namespace rf

@@ -75,6 +75,9 @@ GemmPlan plan_for(int m, int n, int k, int num_sms, int bn, int forced_split) {
 GemmPlan choose_plan(int m, int n, int k, int num_sms, int forced_split) {
     const int fb = forced_block_n();
     if (fb) return plan_for(m, n, k, num_sms, fb, forced_split);
+    // a measured entry for this exact shape beats the model (the caller's explicit split still wins)
+    int tbn = 0, tsplits = 0;
+    if (forced_split <= 0 && rf::tuned_plan_lookup(m, n, k, &tbn, &tsplits)) return GemmPlan{tbn, tsplits, 0.0};
     GemmPlan p128 = plan_for(m, n, k, num_sms, 128, forced_split);
     GemmPlan p256 = plan_for(m, n, k, num_sms, 256, forced_split);
     // Wide tiles halve the A traffic and the MMA instruction count per FLOP; prefer them unless
@@ -230,6 +233,15 @@ int rf_device_status(int* detail) {
         cudaMemset(st->status, 0, sizeof(int));
         return RF_ERR_DEVICE_TIMEOUT;
     }
+    return RF_OK;
+}
+
+int rf_fp8_gemm_get_plan(int m, int n, int k, int* block_n, int* split_k) {
+    if (!shape_ok(m, n, k)) return RF_ERR_BAD_SHAPE;
+    rf::DeviceState* st = rf::device_state();
+    const GemmPlan plan = choose_plan(m, n, k, st ? st->num_sms : 148, 0);
+    if (block_n) *block_n = plan.block_n;
+    if (split_k) *split_k = plan.splits;
     return RF_OK;
 }
 
