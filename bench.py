@@ -622,6 +622,7 @@ def run_gpu_arm(args):
                        "parallelism": "replicas" if world > 1 else "single"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": achieved / fp8_peak,
+                         "frac_of_sustained_peak": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
                          "traffic": (sum(NCU_DRAM_BYTES) / len(NCU_DRAM_BYTES) if not args.shapes else None),
                          "traffic_note": "DRAM bytes per fp8_gemm_kernel launch, mean over the 18 shapes, ncu; "
                                          f"algorithmic mean {sum(gemm_bytes(*x) for x in SWEEP) / len(SWEEP):.0f}",
