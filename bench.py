@@ -305,7 +305,7 @@ def run_extras(args, rank, world, dev, dist, peaks):
     cfg = {"d_hidden": d, "d_expert": f, "n_routed_experts": e, "n_shared_experts": 1, "n_experts_per_token": k,
            "batch_size": 1, "seq_len": t_loc}
     bias = torch.from_numpy(bias_np[order]).to(dev)
-    layer = mg.ExpertParallelMoE(cfg, w, t_loc, dev, router_bias=bias)
+    layer = mg.ExpertParallelMoE(cfg, w, t_loc, dev, router_bias=bias, push_results=not args.ep_pull)
     ms = _timed(lambda: layer.forward(x), 5, 2, dev, world, dist)
     layer.trace = []
     layer.forward(x)
@@ -320,7 +320,8 @@ def run_extras(args, rank, world, dev, dist, peaks):
     out["moe_expert_parallel"] = {
         "config": "32768 tokens, d=7168 f=2048 E=256 top-8 + 1 shared, Zipf(1.1) router bias; experts sharded E/N "
                   "per GPU by a static load-aware placement from one calibration pass; dispatch by peer stores, "
-                  "combine by peer loads",
+                  + ("combine by peer loads" if args.ep_pull else
+                     "expert outputs pushed home by the second GEMM's epilogue (peer stores), local combine"),
         "ms_per_layer": ms, "tokens_per_s": t_total / (ms * 1e-3), "tflops_total": fl / (ms * 1e-3) / 1e12,
         "stage_ms_rank0": stages, "scaling": "strong", "rows_per_gpu_max": mx.item(), "rows_per_gpu_mean": sm.item() / world,
         "imbalance_max_over_mean": mx.item() / (sm.item() / world)}
@@ -390,6 +391,28 @@ def run_moe_only(args):
                      "unit": "TFLOP/s", "frac": fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "traffic": None,
                      "kernel": "moe_gemm_kernel"},
         "gpu_launches": 18 * steps}), flush=True)
+
+
+def run_multi_gpu_only(args):
+    """The multi-GPU workloads alone (expert-parallel MoE, N-split GEMM; plus the single-GPU MoE replica):
+    one JSON line with the `extras` object of the full run.  Launch under torchrun for N > 1."""
+    import torch
+    import torch.distributed as dist
+    from radeonflow_kernels_b200 import build
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    build.build()
+    extras = run_extras(args, rank, world, dev, dist, measured_peaks())
+    if rank == 0:
+        print(json.dumps({"workload": "multi-gpu extras", "n_gpus": world, "extras": extras}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def _lib_handle():
@@ -649,7 +672,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE and N-split GEMM workloads")
-    ap.add_argument("--workload", default="sweep", choices=["sweep", "moe"],
+    ap.add_argument("--ep-pull", action="store_true",
+                    help="expert-parallel MoE: combine pulls the expert outputs instead of fc2 pushing them")
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "moe", "multi"],
                     help="sweep = the FP8 GEMM benchmark line (default); moe = only the single-GPU MoE layer "
                          "(profiling aid: prints its own line, metric moe_layer_tokens_per_s)")
     ap.add_argument("--shapes", default="", help="restrict the sweep, e.g. 6144x4608x7168,1024x512x7168 "
@@ -665,6 +690,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "moe":
         run_moe_only(args)
+    elif args.workload == "multi":
+        run_multi_gpu_only(args)
     else:
         run_gpu_arm(args)
 

@@ -347,11 +347,25 @@ int rf_moe_ep_layout(const int *counts_all_dev, int rank, int world, int n_exper
 /* Dispatch: the token-row gather of expand_input (src/moe/moe_topk_kernel.cpp:174-213) writing
  * directly into the owner ranks' receive buffers `recv_x_all[r]` (fp16 [capacity, d_hidden]).
  * pair_rank / pair_row [n_pairs] record the destination of every locally sorted pair.  Rank r
- * sends to rank r+1 first, then r+2, ... so the senders never all target one GPU.         */
+ * sends to rank r+1 first, then r+2, ... so the senders never all target one GPU.
+ * recv_meta_all (may be NULL): every rank's int32 [capacity] return-address table; beside row i of
+ * recv_x_all[q] the sender writes recv_meta_all[q][i] = (rank << 28) | p, p = position of the pair in
+ * the sender's expert-sorted order - the row_dest_dev input of rf_moe_grouped_gemm_scatter.       */
 int rf_moe_ep_dispatch(const void *x, const int *permuted_experts, const int *permuted_rows,
                        const int *first_token_offset, const int *send_base, int n_tokens, int n_pairs, int d_hidden,
-                       int n_experts, int rank, int world, void *const *recv_x_all, int *pair_rank, int *pair_row,
-                       rf_stream_t stream);
+                       int n_experts, int rank, int world, void *const *recv_x_all, void *const *recv_meta_all,
+                       int *pair_rank, int *pair_row, rf_stream_t stream);
+
+/* The experts' second GEMM fused with the way back (no reference counterpart: the reference is single-GPU;
+ * it is the grouped fc2 of src/moe/moe.cpp:244-248 whose epilogue performs the row scatter that
+ * reduce_output's gather, src/moe/moe_topk_kernel.cpp:215-251, would otherwise do over NVLink).
+ * out row i = x[i,:] . w[group(i)] is stored, by peer stores from the GEMM's epilogue, to row
+ * (row_dest_dev[i] & 0x0FFFFFFF) of dest_all[row_dest_dev[i] >> 28] (fp16 [*, n_dim]).  After a
+ * rendezvous every rank holds its own pairs' expert outputs in expert-sorted order and finishes with the
+ * local rf_moe_combine.                                                                          */
+int rf_moe_grouped_gemm_scatter(const void *x, int n_rows, const void *const *w_ptrs_host,
+                                const int *group_offsets_dev, int n_groups, int n_dim, int k_dim,
+                                const int *row_dest_dev, void *const *dest_all, int world, rf_stream_t stream);
 
 /* Combine: reduce_output (src/moe/moe_topk_kernel.cpp:215-251) reading each expert output row
  * from its owner rank's `y_all[r]` (fp16 [capacity, d_hidden]) over NVLink.  shared_fc2_output

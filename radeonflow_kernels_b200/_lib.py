@@ -153,7 +153,9 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_moe_ep_layout.restype = ci
     L.rf_moe_ep_layout.argtypes = [vp, ci, ci, ci, vp, vp, vp]
     L.rf_moe_ep_dispatch.restype = ci
-    L.rf_moe_ep_dispatch.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, pvp, vp, vp, vp]
+    L.rf_moe_ep_dispatch.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, pvp, pvp, vp, vp, vp]
+    L.rf_moe_grouped_gemm_scatter.restype = ci
+    L.rf_moe_grouped_gemm_scatter.argtypes = [vp, ci, pvp, vp, ci, ci, ci, vp, pvp, ci, vp]
     L.rf_moe_ep_combine.restype = ci
     L.rf_moe_ep_combine.argtypes = [pvp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, vp]
 

@@ -154,7 +154,8 @@ struct StageTimer {
 // One grouped GEMM: rows of `x` [n_rows, k] by per-group weights; `offsets_dev` has n_groups+1 entries.
 int grouped_gemm(int mode, const void* x, int n_rows, const void* const* w_host, const void* const* w2_host,
                  int n_groups, const int* offsets_dev, int n_out, int k, const float* bias, void* out, const Aux& aux,
-                 DeviceState* st, cudaStream_t stream) {
+                 DeviceState* st, cudaStream_t stream, const int* scatter_meta = nullptr,
+                 const rf::PeerPtrs* scatter_dst = nullptr) {
     if (n_rows <= 0) return RF_OK;
     const CUtensorMap* maps;
     const CUtensorMap* maps2 = nullptr;
@@ -169,7 +170,7 @@ int grouped_gemm(int mode, const void* x, int n_rows, const void* const* w_host,
     if (!rf::encode_tma_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)n_rows, (uint64_t)k, (uint64_t)k * 2,
                            128, 64, true))
         return RF_ERR_CUDA;
-    const bool tma_store = (n_out % 64) == 0;
+    const bool tma_store = (n_out % 64) == 0 && !scatter_meta;
     if (tma_store) {
         if (!rf::encode_tma_2d(&to, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, (uint64_t)n_rows, (uint64_t)n_out,
                                (uint64_t)n_out * 2, 32, 64, true))
@@ -193,6 +194,9 @@ int grouped_gemm(int mode, const void* x, int n_rows, const void* const* w_host,
     p.n_out = n_out;
     p.k = k;
     p.tma_store = tma_store ? 1 : 0;
+    p.scatter_meta = scatter_meta;
+    if (scatter_dst) p.scatter_dst = *scatter_dst;
+    else memset(&p.scatter_dst, 0, sizeof p.scatter_dst);
     p.status = st->status;
     if (rf::moe_gemm_launch(mode, ta, to, p, st->num_sms, stream) != cudaSuccess) return RF_ERR_CUDA;
     return RF_OK;
@@ -450,6 +454,26 @@ int rf_moe_grouped_gemm(const void* x, int n_rows, const void* const* w_ptrs_hos
     return grouped_gemm(w2_ptrs_host ? rf::kMoeGemmSwiglu : rf::kMoeGemmPlain, x, n_rows, w_ptrs_host, w2_ptrs_host,
                         n_groups, group_offsets_dev, n_dim, k_dim, nullptr, out, aux, st,
                         reinterpret_cast<cudaStream_t>(stream));
+}
+
+int rf_moe_grouped_gemm_scatter(const void* x, int n_rows, const void* const* w_ptrs_host,
+                                const int* group_offsets_dev, int n_groups, int n_dim, int k_dim,
+                                const int* row_dest_dev, void* const* dest_all, int world, rf_stream_t stream) {
+    if (!x || !w_ptrs_host || !group_offsets_dev || !row_dest_dev || !dest_all) return RF_ERR_NULL_POINTER;
+    if (n_rows < 0 || n_groups < 1 || n_groups > 1024 || n_dim <= 0 || n_dim % 64 != 0 || k_dim <= 0 ||
+        k_dim % 64 != 0 || world < 1 || world > 8)
+        return RF_ERR_BAD_SHAPE;
+    rf::PeerPtrs pp;
+    for (int i = 0; i < 8; ++i) pp.p[i] = dest_all[i < world ? i : 0];
+    for (int i = 0; i < world; ++i)
+        if (!pp.p[i] || ((uintptr_t)pp.p[i] & 15)) return RF_ERR_NULL_POINTER;
+    DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    Aux aux;
+    if (!carve_aux(&aux, n_rows, n_groups)) return RF_ERR_CUDA;
+    return grouped_gemm(rf::kMoeGemmPlain, x, n_rows, w_ptrs_host, nullptr, n_groups, group_offsets_dev, n_dim, k_dim,
+                        nullptr, const_cast<void*>(x), aux, st, reinterpret_cast<cudaStream_t>(stream), row_dest_dev,
+                        &pp);
 }
 
 int rf_moe_router_gemm(const void* x, const void* router_weight, const float* router_bias, int n_tokens,

@@ -31,9 +31,15 @@ ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_
     const int per = n_experts / world;
     int t = 0, before_me = 0;
     if (e < n_experts) {
-        for (int s = 0; s < world; ++s) {
+        // Rows of one expert are ordered by source rank starting at the owner: q, q+1, ... (mod world).
+        // The owners then walk their rows, and return the results, towards different GPUs at any moment.
+        const int q = e / per;
+        const int my_pos = (rank - q + world) % world;
+        for (int j = 0; j < world; ++j) {
+            int s = q + j;
+            if (s >= world) s -= world;
             const int c = counts_all[s * n_experts + e];
-            if (s < rank) before_me += c;
+            if (j < my_pos) before_me += c;
             t += c;
         }
         tot[e] = t;
@@ -59,8 +65,8 @@ __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted_experts,
                    const int* __restrict__ permuted_rows, const int* __restrict__ first_token_offset,
                    const int* __restrict__ send_base, int n_tokens, int n_pairs, int vec_per_row,
-                   int experts_per_rank, int rank, int world, PeerPtrs recv_x, int* __restrict__ pair_rank,
-                   int* __restrict__ pair_row) {
+                   int experts_per_rank, int rank, int world, PeerPtrs recv_x, PeerPtrs recv_meta, int with_meta,
+                   int* __restrict__ pair_rank, int* __restrict__ pair_row) {
     // Pairs are sorted by expert, hence by destination rank.  Every source starts with a different
     // destination (rank+1, rank+2, ...), so at any moment the senders target different GPUs instead of
     // all writing into the same one.
@@ -86,6 +92,7 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted
         if (threadIdx.x == 0) {
             pair_rank[p] = q;
             pair_row[p] = row;
+            if (with_meta) static_cast<int*>(pick_peer(recv_meta, q))[row] = (rank << kEpMetaSlotBits) | p;
         }
     }
 }
@@ -221,7 +228,8 @@ cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int
 cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, const int* permuted_rows,
                                    const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs,
                                    int row_bytes, int experts_per_rank, int rank, int world, const PeerPtrs& recv_x,
-                                   int* pair_rank, int* pair_row, int num_sms, cudaStream_t stream) {
+                                   const PeerPtrs* recv_meta, int* pair_rank, int* pair_row, int num_sms,
+                                   cudaStream_t stream) {
     const int vec = row_bytes / 16;
     if (n_pairs == 0) return cudaSuccess;
     int blocks = num_sms * 8;
@@ -229,6 +237,7 @@ cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, c
     ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(x), permuted_experts,
                                                              permuted_rows, first_token_offset, send_base, n_tokens,
                                                              n_pairs, vec, experts_per_rank, rank, world, recv_x,
+                                                             recv_meta ? *recv_meta : recv_x, recv_meta ? 1 : 0,
                                                              pair_rank, pair_row);
     return cudaGetLastError();
 }

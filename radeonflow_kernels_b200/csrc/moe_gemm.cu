@@ -47,6 +47,15 @@ __device__ __forceinline__ float silu_fp16_rounded(float g) {
     return __half2float(__float2half_rn(s));
 }
 
+// One of the (at most 8) peer pointers, without indexing the kernel-parameter struct dynamically.
+__device__ __forceinline__ void* pick_peer(const PeerPtrs& pp, int q) {
+    void* r = pp.p[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+        if (q == i) r = pp.p[i];
+    return r;
+}
+
 // Work item -> (row tile, column block).  Items walk one chunk (up to kMoeChunkTiles row tiles of one
 // group, built by tile_list_kernel) for one column block, then the next column block of the same chunk:
 // the CTAs running at the same time share that group's weight column block, and the chunk's A tiles stay
@@ -210,6 +219,14 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const bool full_slab = rows_valid >= 32;
             const bool my_row_ok = lane < rows_valid;
             const uint32_t tbase = lane_addr + buf * BN;
+            // scatter mode: this thread's row goes to a row of another (or this) GPU's matrix
+            const bool scatter = MODE == kMoeGemmPlain && p.scatter_meta != nullptr;
+            __half* scatter_row = nullptr;
+            if (scatter && my_row_ok) {
+                const int meta = __ldg(p.scatter_meta + slab_row0 + lane);
+                scatter_row = static_cast<__half*>(pick_peer(p.scatter_dst, meta >> kEpMetaSlotBits)) +
+                              (size_t)(meta & ((1 << kEpMetaSlotBits) - 1)) * p.n_out;
+            }
 
             // 64 output columns (one 128-byte slab row) per iteration
             constexpr int OUT_COLS = SWIGLU ? 64 : 128;          // per epilogue warp
@@ -247,7 +264,27 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                     for (int j = 0; j < 16; ++j) packed[h * 16 + j] = pack_f16x2(v[2 * j], v[2 * j + 1]);
                 }
                 if (out_col >= p.n_out || rows_valid <= 0) continue;
-                if (p.tma_store && full_slab) {
+                if (scatter) {
+                    // Through the warp's slab, so that every store instruction writes four whole 128-byte
+                    // row segments (8 lanes each) instead of 32 scattered 16-byte pieces: over NVLink the
+                    // payload per transaction decides the bandwidth.
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        st_shared_v4(my_row + ((j ^ (lane & 7)) << 4), packed[4 * j], packed[4 * j + 1],
+                                     packed[4 * j + 2], packed[4 * j + 3]);
+                    __syncwarp();
+                    const int c = lane & 7;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = 4 * i + (lane >> 3);
+                        const unsigned long long base =
+                            __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(scatter_row), r);
+                        const uint4 v = ld_shared_v4(slab + r * 128 + ((c ^ (r & 7)) << 4));
+                        if (r < rows_valid)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(base) + out_col + 8 * c) = v;
+                    }
+                } else if (p.tma_store && full_slab) {
                     if (lane == 0) tma_store_wait_read<0>();
                     __syncwarp();
 #pragma unroll

@@ -32,11 +32,15 @@ struct PeerPtrs {
 cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int n_experts, int* send_base,
                                  int* recv_offsets, cudaStream_t stream);
 // Copies the token row of every local (token, expert) pair into the owner rank's receive buffer
-// (peer stores) and records where it went (pair_rank, pair_row).
+// (peer stores) and records where it went (pair_rank, pair_row).  With `recv_meta` != nullptr it also
+// writes, beside every row it sends, the return address of the row's result: (this rank << 28) | p, p = the
+// pair's position in this rank's expert-sorted order (kEpMetaSlotBits bits).
+constexpr int kEpMetaSlotBits = 28;
 cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, const int* permuted_rows,
                                    const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs,
                                    int row_bytes, int experts_per_rank, int rank, int world, const PeerPtrs& recv_x,
-                                   int* pair_rank, int* pair_row, int num_sms, cudaStream_t stream);
+                                   const PeerPtrs* recv_meta, int* pair_rank, int* pair_row, int num_sms,
+                                   cudaStream_t stream);
 // out[t] = fp16(sum_i w_i * Y_{rank_i}[row_i] + shared[t]) with Y rows read from the owner ranks (peer loads).
 cudaError_t moe_ep_combine_launch(const PeerPtrs& y, const void* shared_out, const int* rev, const void* weights,
                                   const int* pair_rank, const int* pair_row, int n_tokens, int top_k, int row_bytes,
@@ -73,6 +77,11 @@ struct MoeGemmParams {
     const CUtensorMap* b2_maps; // second weight per group (SwiGLU mode), else unused
     const float* bias;          // router mode: optional fp32 [n_out]
     void* out;                  // fp16 [rows, n_out]
+    // Plain mode only, optional: row r of the result is stored to row (scatter_meta[r] & slot mask) of the
+    // fp16 [*, n_out] matrix scatter_dst.p[scatter_meta[r] >> kEpMetaSlotBits] instead of out[r] (peer stores:
+    // the expert outputs travel back to the GPUs that own the tokens from the GEMM's own epilogue).
+    const int* scatter_meta;
+    PeerPtrs scatter_dst;
     int n_out;                  // output columns
     int k;                      // reduction length (multiple of 64)
     int tma_store;              // 1: full 32-row slabs leave through the output tensor map

@@ -80,8 +80,8 @@ int rf_moe_ep_layout(const int* counts_all_dev, int rank, int world, int n_exper
 
 int rf_moe_ep_dispatch(const void* x, const int* permuted_experts, const int* permuted_rows,
                        const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs, int d_hidden,
-                       int n_experts, int rank, int world, void* const* recv_x_all, int* pair_rank, int* pair_row,
-                       rf_stream_t stream) {
+                       int n_experts, int rank, int world, void* const* recv_x_all, void* const* recv_meta_all,
+                       int* pair_rank, int* pair_row, rf_stream_t stream) {
     if (!x || !permuted_experts || !permuted_rows || !first_token_offset || !send_base || !recv_x_all || !pair_rank ||
         !pair_row)
         return RF_ERR_NULL_POINTER;
@@ -94,9 +94,16 @@ int rf_moe_ep_dispatch(const void* x, const int* permuted_experts, const int* pe
     for (int i = 0; i < 8; ++i) pp.p[i] = recv_x_all[i < world ? i : 0];
     for (int i = 0; i < world; ++i)
         if (!pp.p[i] || ((uintptr_t)pp.p[i] & 15)) return RF_ERR_NULL_POINTER;
+    rf::PeerPtrs pm;
+    if (recv_meta_all) {
+        if (n_pairs >= (1 << rf::kEpMetaSlotBits)) return RF_ERR_BAD_SHAPE;
+        for (int i = 0; i < 8; ++i) pm.p[i] = recv_meta_all[i < world ? i : 0];
+        for (int i = 0; i < world; ++i)
+            if (!pm.p[i] || ((uintptr_t)pm.p[i] & 3)) return RF_ERR_NULL_POINTER;
+    }
     return rf::moe_ep_dispatch_launch(x, permuted_experts, permuted_rows, first_token_offset, send_base, n_tokens,
-                                      n_pairs, d_hidden * 2, n_experts / world, rank, world, pp, pair_rank, pair_row,
-                                      st->num_sms,
+                                      n_pairs, d_hidden * 2, n_experts / world, rank, world, pp,
+                                      recv_meta_all ? &pm : nullptr, pair_rank, pair_row, st->num_sms,
                                       reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
                ? RF_OK : RF_ERR_CUDA;
 }

@@ -25,18 +25,21 @@ def ep_layout_reference(counts_all: np.ndarray, rank: int):
     """numpy statement of what ``rf_moe_ep_layout`` computes on the device.
 
     counts_all [world, E]: row s = number of (token, expert) pairs per global expert on source rank s.
-    Expert e is owned by rank e // (E // world).  In the owner's receive buffer rows are ordered by
-    (expert, source rank, source-local order).  Returns (send_base [E], recv_offsets [E/world + 1]).
+    Expert e is owned by rank q = e // (E // world).  In the owner's receive buffer rows are ordered by
+    (expert, source rank in the rotated order q, q+1, ..., q+world-1 mod world, source-local order): every
+    owner walks its experts' rows starting with its own tokens, so at any moment the owners return results
+    to different GPUs.  Returns (send_base [E], recv_offsets [E/world + 1]).
     """
     counts_all = np.asarray(counts_all, dtype=np.int64)
     world, n_experts = counts_all.shape
     per = n_experts // world
     tot = counts_all.sum(axis=0)
-    before_me = counts_all[:rank].sum(axis=0)
     send_base = np.zeros(n_experts, dtype=np.int64)
     for e in range(n_experts):
-        first = (e // per) * per
-        send_base[e] = tot[first:e].sum() + before_me[e]
+        q = e // per
+        first = q * per
+        before_me = sum(int(counts_all[(q + j) % world, e]) for j in range((rank - q) % world))
+        send_base[e] = tot[first:e].sum() + before_me
     recv = np.concatenate([[0], np.cumsum(tot[rank * per:(rank + 1) * per])])
     return send_base.astype(np.int32), recv.astype(np.int32)
 
@@ -162,9 +165,15 @@ class ExpertParallelMoE:
     'experts.{j}.{0,1,2}.weight' for the LOCAL experts j = 0..E/world-1 (global id rank*E/world + j).
     Every rank feeds its own ``n_tokens`` tokens.  ``capacity`` = rows the receive buffers hold
     (default: worst case, every pair of every rank lands here).
+
+    ``push_results`` (default): the experts' second GEMM stores every output row from its epilogue straight
+    into the GPU that owns the token (`rf_moe_grouped_gemm_scatter`), so the transfer back overlaps the GEMM
+    tile by tile and the final combine is local.  False: the outputs stay on the expert's GPU and the
+    combine kernel pulls them over NVLink (`rf_moe_ep_combine`).
     """
 
-    def __init__(self, config, weights, n_tokens: int, device, group=None, capacity=None, router_bias=None):
+    def __init__(self, config, weights, n_tokens: int, device, group=None, capacity=None, router_bias=None,
+                 push_results: bool = True):
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -182,6 +191,7 @@ class ExpertParallelMoE:
         self.capacity = int(capacity) if capacity else self.n_pairs * self.world
         self.weights = weights
         self.router_bias = router_bias
+        self.push_results = bool(push_results)
         self.trace = None           # set to [] to time the stages of the next forward
         dev, T, K, E, d, f = self.device, self.T, self.K, self.E, self.d, self.f
         i32, f16 = torch.int32, torch.float16
@@ -220,7 +230,13 @@ class ExpertParallelMoE:
         if self.world > 1:
             dist.barrier(group=group)           # every rank's sync area is zero before anyone raises a flag
         self.recv_x = PeerBuffer(self.capacity * d * 2, dev, group)
-        self.y = PeerBuffer(self.capacity * d * 2, dev, group)
+        if self.push_results:
+            # results come home by peer stores: one row per local (token, expert) pair, expert-sorted order
+            self.y = PeerBuffer(max(16, self.n_pairs * d * 2), dev, group)
+            self.recv_meta = PeerBuffer(4 * self.capacity, dev, group)
+        else:
+            self.y = PeerBuffer(self.capacity * d * 2, dev, group)
+            self.recv_meta = None
 
         def ptr_array(tensors):
             arr = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
@@ -264,7 +280,8 @@ class ExpertParallelMoE:
         side = ctypes.c_void_p(self.side_stream.cuda_stream)
         chk(L.rf_moe_ep_dispatch(x.data_ptr(), self.perm_experts.data_ptr(), self.perm_rows.data_ptr(),
                                  self.first.data_ptr(), self.send_base.data_ptr(), T, T * K, d, E, self.rank, self.world,
-                                 self.recv_x.ptr_array, self.pair_rank.data_ptr(), self.pair_row.data_ptr(), side),
+                                 self.recv_x.ptr_array, self.recv_meta.ptr_array if self.push_results else None,
+                                 self.pair_rank.data_ptr(), self.pair_row.data_ptr(), side),
             "rf_moe_ep_dispatch")
         self.ev_sent.record(self.side_stream)
         chk(L.rf_moe_grouped_gemm(x.data_ptr(), T, self._s_gate, self._s_up, self.single_offsets.data_ptr(), 1,
@@ -278,11 +295,23 @@ class ExpertParallelMoE:
         chk(L.rf_moe_grouped_gemm(self.recv_x.local_ptr, self.capacity, self._w_gate, self._w_up,
                                   self.recv_offsets.data_ptr(), self.E_loc, f, d, self.h.data_ptr(), s), "routed fc1")
         self._mark("routed fc1")
-        chk(L.rf_moe_grouped_gemm(self.h.data_ptr(), self.capacity, self._w_down, None, self.recv_offsets.data_ptr(),
-                                  self.E_loc, d, f, self.y.local_ptr, s), "routed fc2")
+        if self.push_results:
+            chk(L.rf_moe_grouped_gemm_scatter(self.h.data_ptr(), self.capacity, self._w_down,
+                                              self.recv_offsets.data_ptr(), self.E_loc, d, f,
+                                              self.recv_meta.local_ptr, self.y.ptr_array, self.world, s),
+                "routed fc2 + return")
+        else:
+            chk(L.rf_moe_grouped_gemm(self.h.data_ptr(), self.capacity, self._w_down, None,
+                                      self.recv_offsets.data_ptr(), self.E_loc, d, f, self.y.local_ptr, s),
+                "routed fc2")
         self._mark("routed fc2")
-        self._rendezvous(None, 0)                       # every rank's expert outputs are complete
+        self._rendezvous(None, 0)                       # every rank's expert outputs are complete (and home)
         self._mark("barrier2")
+        if self.push_results:
+            chk(L.rf_moe_combine(self.y.local_ptr, self.sh2.data_ptr(), self.rev.data_ptr(), self.exp_w.data_ptr(),
+                                 T, K, d, self.out.data_ptr(), s), "rf_moe_combine")
+            self._mark("combine")
+            return self.out
         # (Running the shared expert's second GEMM concurrently with this combine and adding its rows
         # afterwards with rf_moe_add_rows was measured: no gain on 8 GPUs, and one more fp16 rounding.)
         chk(L.rf_moe_ep_combine(self.y.ptr_array, self.sh2.data_ptr(), self.rev.data_ptr(), self.exp_w.data_ptr(),
@@ -316,4 +345,6 @@ class ExpertParallelMoE:
     def close(self):
         self.recv_x.close()
         self.y.close()
+        if self.recv_meta is not None:
+            self.recv_meta.close()
         self.sync.close()

@@ -67,12 +67,19 @@ def main():
     for q in range(3):
         wl[f"shared_experts.{q}.weight"] = w[f"shared_experts.{q}.weight"]
     dw = {name: torch.from_numpy(v).to(dev) for name, v in wl.items()}
-    layer = mg.ExpertParallelMoE(cfg, dw, T_loc, dev, router_bias=torch.from_numpy(bias).to(dev))
     x_loc = torch.from_numpy(x[0, rank * T_loc:(rank + 1) * T_loc]).to(dev)
+    # first the variant whose combine pulls the expert outputs over NVLink, then (kept for the checks below)
+    # the default one, whose second expert GEMM pushes its rows home from the epilogue
+    pulled = mg.ExpertParallelMoE(cfg, dw, T_loc, dev, router_bias=torch.from_numpy(bias).to(dev), push_results=False)
+    out_pull = pulled.forward(x_loc).clone()
+    torch.cuda.synchronize()
+    pulled.close()
+    layer = mg.ExpertParallelMoE(cfg, dw, T_loc, dev, router_bias=torch.from_numpy(bias).to(dev))
     for _ in range(2):                           # twice: buffers are reused across steps
         out = layer.forward(x_loc)
     torch.cuda.synchronize()
     assert G.device_status() == 0
+    assert torch.equal(out, out_pull), "push and pull variants must agree bit for bit (same fp32 combine order)"
     # oracle on the full problem, downstream of the logits this rank produced for its tokens
     logits_loc = layer.scores.cpu().numpy()
     ref_logits = om.router_logits(x[0], w["router.weight"], bias)

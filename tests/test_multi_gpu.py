@@ -114,8 +114,9 @@ def test_layout_planner_small_case():
     counts = np.array([[1, 2, 0, 3], [4, 0, 5, 6]])        # 2 ranks, 4 experts (2 per rank)
     sb0, ro0 = ep_layout_reference(counts, 0)
     sb1, ro1 = ep_layout_reference(counts, 1)
-    # owner 0 holds experts 0,1: rows [e0: r0(1) r1(4)] [e1: r0(2) r1(0)]
-    assert sb0.tolist() == [0, 5, 0, 5] and sb1.tolist() == [1, 7, 0, 8]
+    # owner 0 holds experts 0,1, sources in the order 0,1: rows [e0: r0(1) r1(4)] [e1: r0(2) r1(0)]
+    # owner 1 holds experts 2,3, sources in the order 1,0: rows [e2: r1(5) r0(0)] [e3: r1(6) r0(3)]
+    assert sb0.tolist() == [0, 5, 5, 11] and sb1.tolist() == [1, 7, 0, 5]
     assert ro0.tolist() == [0, 5, 7] and ro1.tolist() == [0, 5, 14]
 
 
