@@ -58,6 +58,25 @@ def test_bad_arguments_are_rejected_on_the_host(rf_lib):
     assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 100, 1024, 4) == 0
 
 
+def test_expert_parallel_entries_validate_on_the_host(rf_lib):
+    """The multi-GPU entry points reject bad arguments before any device work (no GPU needed)."""
+    buf = (ctypes.c_char * 4096)()
+    p16 = (ctypes.addressof(buf) + 15) & ~15
+    ptrs = (ctypes.c_void_p * 8)(*([p16] * 8))
+    # scatter GEMM: null tables, bad world, n_dim % 64
+    assert rf_lib.rf_moe_grouped_gemm_scatter(p16, 128, ptrs, p16, 1, 128, 128, None, ptrs, 2, None) == 2
+    assert rf_lib.rf_moe_grouped_gemm_scatter(p16, 128, ptrs, p16, 1, 128, 128, p16, None, 2, None) == 2
+    assert rf_lib.rf_moe_grouped_gemm_scatter(p16, 128, ptrs, p16, 1, 128, 128, p16, ptrs, 9, None) == 1
+    assert rf_lib.rf_moe_grouped_gemm_scatter(p16, 128, ptrs, p16, 1, 100, 128, p16, ptrs, 2, None) == 1
+    # dispatch: experts not divisible by the ranks, rank out of range, missing pointer
+    d = lambda **kw: rf_lib.rf_moe_ep_dispatch(
+        kw.get("x", p16), p16, p16, p16, p16, 64, 256, 128, kw.get("e", 8), kw.get("rank", 0), kw.get("world", 2),
+        ptrs, kw.get("meta", ptrs), p16, p16, None)
+    assert d(e=7) == 1 and d(rank=2) == 1 and d(world=9) == 1
+    assert d(x=None) == 2
+    assert rf_lib.rf_moe_ep_layout(p16, 0, 3, 8, p16, p16, None) == 1      # 8 experts over 3 ranks
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     import pytest
     monkeypatch.setattr(_lib, "_lib", None)
