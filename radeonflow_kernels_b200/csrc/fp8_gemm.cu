@@ -470,7 +470,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 }
             }
         }
-        if (lane == 0) tma_store_wait_all<0>();   // all of this warp's stores are complete before exit
+        // Before exit the warp's slab must have been read by its last store.  Waiting for the writes themselves
+        // is left to grid completion (stream order, or the next kernel's griddepcontrol.wait), except when the
+        // stores go to other GPUs: the barrier that follows an N-split GEMM is taken after the data has landed.
+        if (lane == 0) {
+            if (p.n_dest > 1) tma_store_wait_all<0>();
+            else tma_store_wait_read<0>();
+        }
 #ifdef RF_WAIT_STATS
         if (warp == NUM_NON_EPI_WARPS && lane == 0) {
             RF_STAT_FLUSH(3, w_acc);

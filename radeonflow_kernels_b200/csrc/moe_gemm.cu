@@ -321,7 +321,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
         }
-        if (lane == 0) tma_store_wait_all<0>();
+        if (lane == 0) tma_store_wait_read<0>();   // the slab has been read; the writes complete with the grid
     }
 
     tc_fence_before();
