@@ -125,9 +125,10 @@ int rf_fp8_gemm_colmajor_fnuz(const void *a, const void *b, const float *as, con
  * per call.
  *
  * Limits and rules:
- *  - split_k * m * n * 4 bytes must fit in RF_STATIC_SCRATCH_BYTES (split_k = 0 lets the library
- *    choose; the chosen count is subject to the same check).  Otherwise RF_ERR_WORKSPACE is
- *    returned and a message names the sizes; split_k = 1 never needs scratch.
+ *  - An explicit split_k >= 2 needs split_k * m * n * 4 bytes to fit in RF_STATIC_SCRATCH_BYTES;
+ *    otherwise RF_ERR_WORKSPACE is returned and a message names the sizes.  split_k = 0 lets the
+ *    library choose: when its usual plan for the shape would not fit, it runs the shape unsplit
+ *    (split_k = 1 never needs scratch) instead of refusing.
  *  - The first call on each device looks up the array's device address and sets kernel attributes;
  *    make that first call before starting any stream capture.
  *  - All calls on a device share the one array and it keeps the previous call's slices.  Nothing in

@@ -89,7 +89,12 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
 
     int bn = 128, splits = 1;
     rf::fp8_gemm_plan(m, n, k, sd->num_sms, split_k, &bn, &splits);
-    const size_t need = splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
+    size_t need = splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
+    if (need > kStaticScratchBytes && split_k <= 0) {
+        // the library's own choice must fit the built-in array: fall back to the unsplit plan
+        rf::fp8_gemm_plan(m, n, k, sd->num_sms, 1, &bn, &splits);
+        need = 0;
+    }
     if (need > kStaticScratchBytes) {
         fprintf(stderr,
                 "rf_fp8_gemm_static_scratch: %d K slices of a %d x %d result need %zu bytes of scratch, the built-in "

@@ -47,6 +47,22 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point(rf_lib):
     run_both(rf_lib, 256, 192, 1024, 1, seed=3)        # no scratch needed
 
 
+def test_automatic_split_never_exceeds_the_built_in_array(rf_lib):
+    """1024 x 1536 x 7168: the tuned plan is 3 K slices (18.9 MB of scratch); with split_k = 0 the
+    allocation-free entry must run it unsplit instead of refusing."""
+    m, n, k = 1024, 1536, 7168
+    assert rf_lib.rf_fp8_gemm_choose_split(m, n, k) * m * n * 4 > STATIC_BYTES
+    a, b, a_s, b_s = o.generate_input(m, n, k, 9)
+    da, db, das, dbs = gemm_device_inputs(a, b, a_s, b_s)
+    c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda:0")
+    st = rf_lib.rf_fp8_gemm_static_scratch(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(),
+                                           c.data_ptr(), m, n, k, 0, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    ok, n_bad, max_err = o.check(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a, b, a_s, b_s))
+    assert ok, (n_bad, max_err)
+
+
 def test_sizes_beyond_the_built_in_array_are_rejected(rf_lib):
     m, n, k = 2048, 1024, 1024
     assert 8 * m * n * 4 > STATIC_BYTES
