@@ -320,7 +320,7 @@ def run_extras(args, rank, world, dev, dist, peaks):
     out["moe_expert_parallel"] = {
         "config": "32768 tokens, d=7168 f=2048 E=256 top-8 + 1 shared, Zipf(1.1) router bias; experts sharded E/N "
                   "per GPU by a static load-aware placement from one calibration pass; dispatch by peer stores, "
-                  + ("combine by peer loads" if args.ep_pull else
+                  + ("combine by peer loads" if (args.ep_pull or world == 1) else
                      "expert outputs pushed home by the second GEMM's epilogue (peer stores), local combine"),
         "ms_per_layer": ms, "tokens_per_s": t_total / (ms * 1e-3), "tflops_total": fl / (ms * 1e-3) / 1e12,
         "stage_ms_rank0": stages, "scaling": "strong", "rows_per_gpu_max": mx.item(), "rows_per_gpu_mean": sm.item() / world,

@@ -191,7 +191,8 @@ class ExpertParallelMoE:
         self.capacity = int(capacity) if capacity else self.n_pairs * self.world
         self.weights = weights
         self.router_bias = router_bias
-        self.push_results = bool(push_results)
+        # on one GPU nothing travels: the plain second GEMM (TMA stores) plus the gathering combine is faster
+        self.push_results = bool(push_results) and self.world > 1
         self.trace = None           # set to [] to time the stages of the next forward
         dev, T, K, E, d, f = self.device, self.T, self.K, self.E, self.d, self.f
         i32, f16 = torch.int32, torch.float16

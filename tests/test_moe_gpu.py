@@ -281,3 +281,40 @@ def test_combine_without_shared_then_add_rows(rf_lib):
                                  out3.data_ptr(), None) == 0
     torch.cuda.synchronize()
     assert torch.equal(out1, out3)
+
+
+@pytest.mark.gpu
+def test_grouped_gemm_scatter_equals_plain_grouped_gemm_then_permute(rf_lib):
+    """`rf_moe_grouped_gemm_scatter` (the expert-parallel second GEMM, whose epilogue stores row i to row
+    row_dest[i] of a destination matrix) against the plain grouped GEMM on one GPU: the destination table
+    has one entry (this GPU), ragged groups, an empty group, and a permutation as the return addresses."""
+    k_dim, n_dim = 512, 1024
+    sizes = [300, 0, 129, 1, 640, 77]
+    offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int32)
+    rows = int(offsets[-1])
+    rng = np.random.default_rng(17)
+    x = (rng.standard_normal((rows, k_dim)) * 0.5).astype(np.float16)
+    ws = [torch.from_numpy((rng.standard_normal((k_dim, n_dim)) / k_dim ** 0.5).astype(np.float16)).to(DEV)
+          for _ in sizes]
+    dx = torch.from_numpy(x).to(DEV)
+    doff = torch.from_numpy(offsets).to(DEV)
+    wp = (ctypes.c_void_p * len(ws))(*[w.data_ptr() for w in ws])
+    plain = torch.zeros((rows, n_dim), dtype=torch.float16, device=DEV)
+    assert rf_lib.rf_moe_grouped_gemm(dx.data_ptr(), rows, wp, None, doff.data_ptr(), len(sizes), n_dim, k_dim,
+                                      plain.data_ptr(), None) == 0
+    perm = rng.permutation(rows).astype(np.int32)               # rank 0 in the top bits
+    dperm = torch.from_numpy(perm).to(DEV)
+    canary = 0x7BFF
+    dest = torch.full((rows + 8, n_dim), canary, dtype=torch.int16, device=DEV).view(torch.float16)
+    dests = (ctypes.c_void_p * 1)(dest.data_ptr())
+    assert rf_lib.rf_moe_grouped_gemm_scatter(dx.data_ptr(), rows, wp, doff.data_ptr(), len(sizes), n_dim, k_dim,
+                                              dperm.data_ptr(), dests, 1, None) == 0
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    got = dest.cpu().numpy()
+    assert np.array_equal(got[perm].view(np.uint16), plain.cpu().numpy().view(np.uint16))   # same arithmetic, moved rows
+    assert (got[rows:].view(np.uint16) == canary).all()                                     # nothing past the table
+    ref = np.concatenate([o.linear_fp16(x[offsets[g]:offsets[g + 1]], ws[g].cpu().numpy()) for g in range(len(sizes))
+                          if sizes[g]])
+    ok, nbad, mx = o.check(plain.cpu().numpy(), ref)
+    assert ok, (nbad, mx)
