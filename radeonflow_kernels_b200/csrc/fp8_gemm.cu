@@ -8,9 +8,10 @@
 // One persistent CTA per SM, warp-specialised:
 //   warp 0      TMA producer: A [128 x 128 B] and B [BN x 128 B] tiles, 128-byte
 //               swizzle, into a STAGES-deep shared-memory ring (mbarrier tx counts)
-//   warp 1      MMA issuer: per 128-deep K block, 4 x tcgen05.mma.kind::f8f6f4
-//               (K = 32 each) into one of 512/BN TMEM accumulator buffers, then
-//               tcgen05.commit to free the smem stage and publish the buffer
+//   warps 1, 2  MMA issuers, alternating K blocks: per 128-deep K block, 4 x
+//               tcgen05.mma.kind::f8f6f4 (K = 32 each) into one of 512/BN TMEM
+//               accumulator buffers, then ONE tcgen05.commit that publishes the
+//               buffer (the epilogue, which observes it, frees the smem stage)
 //   warps 4..   epilogue: tcgen05.ld the K block's fp32 partial sums, scale by
 //               the exact fp32 product a_s*b_s and add into a register
 //               accumulator (packed fma.rn.f32x2) while the next K blocks' MMAs run
@@ -51,7 +52,8 @@ constexpr int NUM_NON_EPI_WARPS = 4;
 // TWO_CTA: the tile is 256 x BN per CTA PAIR (2-CTA cluster): each CTA loads its own 128 rows of A and
 // half of the B rows, the leader CTA issues cta_group::2 MMAs (M = 256) whose accumulator rows
 // 0-127 / 128-255 land in the two CTAs' TMEM.  Per SM and K block this moves 32 KB through shared
-// memory each way instead of 48 KB, which is what bounds the 1-CTA tile.
+// memory each way instead of 48 KB; measured, it is still slower than the 1-CTA 128 x 256 tile (the
+// epilogue's promotion work, not shared memory, bounds both), so it is selectable but not the default.
 // MN_MAJOR: operands stored [k][m] and [k][n] (M / N contiguous), the reference's physical layout
 // (src/gemm/gemm_kernel_legacy.cpp:264-268); consumed directly as MN-major UMMA operands, so the
 // reference's transpose pass (src/gemm/gemm_launcher.cpp:55-56) has no counterpart here.
