@@ -251,7 +251,6 @@ def make_moe_weights(torch, dev, d, f, experts, seed, with_router_for=None):
 def run_extras(args, rank, world, dev, dist, peaks):
     """MoE layer tokens/s (single-GPU config and the expert-parallel config) and the N-split GEMM."""
     import torch
-    from oracle import moe as om     # only for the seeded Zipf bias (input generation)
     from radeonflow_kernels_b200 import moe as M, multi_gpu as mg
     out = {}
     f16_peak = peaks["bf16_tflops"]
@@ -283,7 +282,8 @@ def run_extras(args, rank, world, dev, dist, peaks):
     # Static load-aware placement decided before the timed region: one calibration pass of the router
     # and top-k kernels over this run's tokens gives pairs per expert; experts are then renumbered in
     # placement order (router rows and bias permuted), which leaves the layer itself unchanged.
-    bias_np = om.zipf_router_bias(e, 1.1, 17)
+    # load skew: logit bias -1.1 * ln(1 + rank_e) with a seeded random rank per expert (Zipf(1.1) popularity)
+    bias_np = (-1.1 * np.log1p(np.random.default_rng(17).permutation(e).astype(np.float64))).astype(np.float32)
     g.manual_seed(100 + rank)
     x = torch.randn((t_loc, d), device=dev, dtype=torch.float16, generator=g)
     g.manual_seed(13)
@@ -424,7 +424,6 @@ def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
 
-    from oracle import fp8_gemm as o  # input generator + CPU baseline leg only
     from radeonflow_kernels_b200 import _lib, build
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
