@@ -1,5 +1,6 @@
 """Multi-GPU paths.  CPU part: two gloo ranks exercise the expert-parallel exchange protocol (count
-all-gather, host-side layout planner, row exchange) against the single-process oracle.  GPU part:
+all-gather, host-side layout planner, row exchange, and both ways back: owners pull the expert rows, or the
+experts push them to the return address that travelled with each row) against the single-process oracle.  GPU part:
 torch.distributed.run launches tests/mgpu_worker.py with one rank per visible GPU (one is enough to
 run the peer-memory code path; more exercise NVLink)."""
 import os
@@ -51,19 +52,26 @@ dest_row = send_base[pe] + (np.arange(len(pe)) - first[pe])
 owner = pe // e_loc
 cap = int(counts_all.sum())
 recv = torch.zeros((cap, d))
+recv_meta = np.full(cap, -1, dtype=np.int64)
 for q in range(world):            # emulate the peer stores with point-to-point sends
     sel = np.nonzero(owner == q)[0]
-    payload = torch.cat([torch.from_numpy(dest_row[sel].astype(np.float32))[:, None], rows[sel]], dim=1)
+    # beside every row travels its destination row and its return address (rank << 28) | sorted position
+    meta_sel = ((rank << 28) | sel).astype(np.float64)
+    payload = torch.cat([torch.from_numpy(dest_row[sel].astype(np.float32))[:, None], rows[sel],
+                         torch.from_numpy(meta_sel)[:, None].float() * 0], dim=1)
+    payload = payload.double()
+    payload[:, -1] = torch.from_numpy(meta_sel)
     sizes = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
     dist.all_gather(sizes, torch.tensor([len(sel)], dtype=torch.int64))
     if q == rank:
         for s in range(world):
             n = int(sizes[s])
-            buf = payload if s == rank else torch.zeros((n, d + 1))
+            buf = payload if s == rank else torch.zeros((n, d + 2), dtype=torch.float64)
             if s != rank and n:
                 dist.recv(buf, src=s)
             if n:
-                recv[buf[:, 0].long()] = buf[:, 1:]
+                recv[buf[:, 0].long()] = buf[:, 1:d + 1].float()
+                recv_meta[buf[:, 0].long().numpy()] = buf[:, -1].long().numpy()
     elif len(sel):
         dist.send(payload, dst=q)
 # experts on the received rows
@@ -93,6 +101,37 @@ for i in range(K):
 ref = om.moe_stages(x[0], w, E, K, router_bias=bias)["final_output"][rank * T_loc:(rank + 1) * T_loc]
 ok, nbad, mx = om.check(out.astype(np.float16), ref)
 assert ok, (nbad, mx)
+# push variant: every owner returns row i of its y to row (meta & mask) of rank (meta >> 28)'s buffer,
+# which is laid out in that rank's expert-sorted order; the combine is then local (rev only)
+n_rows = int(recv_off[-1])
+assert (recv_meta[:n_rows] >= 0).all()
+home = torch.zeros((len(pe), d))
+for q in range(world):                      # q = the owner whose results are being returned
+    if q == rank:
+        dst_rank = recv_meta[:n_rows] >> 28
+        slot = recv_meta[:n_rows] & ((1 << 28) - 1)
+        for s in range(world):
+            sel = np.nonzero(dst_rank == s)[0]
+            msg = torch.cat([torch.from_numpy(slot[sel].astype(np.float64))[:, None],
+                             torch.from_numpy(y[sel].astype(np.float64))], dim=1)
+            if s == rank:
+                home[msg[:, 0].long()] = msg[:, 1:].float()
+            else:
+                dist.send(torch.tensor([len(sel)], dtype=torch.int64), dst=s)
+                if len(sel):
+                    dist.send(msg, dst=s)
+    else:
+        n = torch.zeros(1, dtype=torch.int64)
+        dist.recv(n, src=q)
+        if int(n):
+            msg = torch.zeros((int(n), d + 1), dtype=torch.float64)
+            dist.recv(msg, src=q)
+            home[msg[:, 0].long()] = msg[:, 1:].float()
+out2 = sh.copy()
+for i in range(K):
+    p = rev[i * T_loc + np.arange(T_loc)]
+    out2 += wts[p][:, None] * home[p].numpy()
+assert np.array_equal(out2.astype(np.float16), out.astype(np.float16)), "push and pull protocols must agree"
 print("GLOO OK", rank)
 '''
 
