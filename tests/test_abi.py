@@ -58,6 +58,21 @@ def test_bad_arguments_are_rejected_on_the_host(rf_lib):
     assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 100, 1024, 4) == 0
 
 
+def test_public_header_compiles_as_c_and_cpp(tmp_path):
+    """include/rf_b200.h is what a C or C++ caller of the reference binds against: plain C99, no CUDA headers."""
+    import shutil
+    import subprocess
+    hdr = os.path.join(ROOT, "include", "rf_b200.h")
+    for compiler, std, ext in (("gcc", "-std=c99", "c"), ("g++", "-std=c++17", "cpp")):
+        if not shutil.which(compiler):
+            continue
+        src = tmp_path / f"t.{ext}"
+        src.write_text(f'#include "{hdr}"\nint main(void) {{ PerfMetrics m; m.count = 0; return RF_OK + m.count; }}\n')
+        res = subprocess.run([compiler, std, "-Wall", "-Wextra", "-pedantic", "-Werror", "-c", str(src), "-o",
+                              str(tmp_path / f"t_{ext}.o")], capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
+
+
 def test_expert_parallel_entries_validate_on_the_host(rf_lib):
     """The multi-GPU entry points reject bad arguments before any device work (no GPU needed)."""
     buf = (ctypes.c_char * 4096)()
