@@ -57,7 +57,10 @@ constexpr int NUM_NON_EPI_WARPS = 4;
 // MN_MAJOR: operands stored [k][m] and [k][n] (M / N contiguous), the reference's physical layout
 // (src/gemm/gemm_kernel_legacy.cpp:264-268); consumed directly as MN-major UMMA operands, so the
 // reference's transpose pass (src/gemm/gemm_launcher.cpp:55-56) has no counterpart here.
-template <int BN, int STAGES, bool TWO_CTA = false, bool MN_MAJOR = false>
+// SLABS: store slabs per epilogue warp.  With two, the second 64-column chunk of a tile is staged while the
+// TMA is still reading the first; worth its 32 KB of shared memory (one pipeline stage fewer) only when K is
+// short and the per-tile store is a large share of the tile's time.
+template <int BN, int STAGES, bool TWO_CTA = false, bool MN_MAJOR = false, int SLABS = 1>
 struct GemmCfg {
     static constexpr int kBN = BN;
     static constexpr int kStages = STAGES;
@@ -75,9 +78,11 @@ struct GemmCfg {
     static constexpr int kTmemBufs = 512 / BN;                // accumulator buffers in flight
     static constexpr int kTmemCols = kTmemBufs * BN;          // all 512 TMEM columns
     static constexpr int kBarBytes = (3 * STAGES + 2 * kTmemBufs) * 8 + 16;
-    static constexpr int kSlabBytes = 32 * 128;               // per epilogue warp: 32 rows x 128 B, swizzled
+    static constexpr int kSlabBytes = 32 * 128;               // one slab: 32 rows x 128 B, swizzled
+    static constexpr int kSlabs = SLABS;                      // slabs per epilogue warp
+    static_assert(SLABS == 1 || SLABS == 2, "one or two store slabs per warp");
     static constexpr int kSmemBytes =
-        STAGES * kStageBytes + kEpiWarps * kSlabBytes + kBarBytes + 1024;       // + alignment slack
+        STAGES * kStageBytes + kEpiWarps * kSlabs * kSlabBytes + kBarBytes + 1024;       // + alignment slack
     // The epilogue (64 or 128 accumulators per thread plus staging) wants more than the 168 registers a
     // 384-thread CTA starts with, the producer warpgroup far fewer: registers are rebalanced.
     static constexpr bool kRebalanceRegs = true;
@@ -122,7 +127,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     // 128-byte-swizzled tiles need 1024-byte alignment.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t slab_base = smem_base + STAGES * Cfg::kStageBytes;
-    const uint32_t bar_base = slab_base + Cfg::kEpiWarps * Cfg::kSlabBytes;
+    const uint32_t bar_base = slab_base + Cfg::kEpiWarps * Cfg::kSlabs * Cfg::kSlabBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
@@ -320,6 +325,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         const int row_in_tile = quad * 32 + lane;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
         uint32_t it = 0;
+        uint32_t n_stores = 0;        // tile-store chunks issued by this warp so far
         bool ok = true;
         long long w_acc = 0, w_total = 0; (void)w_acc; (void)w_total;
 #ifdef RF_WAIT_STATS
@@ -414,14 +420,20 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             // shared-memory slab and one lane hands the slab to the TMA, which writes
             // full 128-byte row segments and clips rows >= m / columns >= n.
             {
-                const uint32_t slab = slab_base + ew * Cfg::kSlabBytes;
-                const uint32_t my_row = slab + lane * 128;
+                // consecutive stores of this warp alternate over its kSlabs slabs (n_stores counts them across
+                // tiles, so skipped chunks of a ragged tile cannot break the alternation); before a slab is
+                // rewritten, the store that last read it (kSlabs commit groups ago) must have finished reading
+                constexpr int SL = Cfg::kSlabs;
+                const uint32_t slab0 = slab_base + ew * SL * Cfg::kSlabBytes;
                 const int slab_row0 = cta_m_blk * BM + quad * 32;
                 if (p.splits == 1) {
 #pragma unroll
                     for (int ch = 0; ch < CPT / 64; ++ch) {
                         if (col0 + ch * 64 >= p.n) break;
-                        if (lane == 0) tma_store_wait_read<0>();   // previous store has drained the slab
+                        const uint32_t slab = slab0 + (n_stores % SL) * Cfg::kSlabBytes;
+                        ++n_stores;
+                        const uint32_t my_row = slab + lane * 128;
+                        if (lane == 0) tma_store_wait_read<SL - 1>();
                         __syncwarp();
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -453,7 +465,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #pragma unroll
                     for (int ch = 0; ch < CPT / 32; ++ch) {
                         if (col0 + ch * 32 >= p.n) break;
-                        if (lane == 0) tma_store_wait_read<0>();
+                        const uint32_t slab = slab0 + (n_stores % SL) * Cfg::kSlabBytes;
+                        ++n_stores;
+                        const uint32_t my_row = slab + lane * 128;
+                        if (lane == 0) tma_store_wait_read<SL - 1>();
                         __syncwarp();
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -542,6 +557,7 @@ fnuz_check_kernel(const uint4* __restrict__ bytes, size_t n_vec, int* status) {
 
 using Cfg128 = GemmCfg<128, 6>;
 using Cfg256 = GemmCfg<256, 4>;
+using Cfg256ShortK = GemmCfg<256, 3, false, false, 2>;     // K <= 512: tiles of at most four K blocks
 using CfgPair = GemmCfg<256, 6, true>;      // 256 x 256 tile per CTA pair
 using Cfg128Mn = GemmCfg<128, 6, false, true>;
 using Cfg256Mn = GemmCfg<256, 4, false, true>;
@@ -554,6 +570,16 @@ bool overlap_launches() {
         return !(e && e[0] == '0');
     }();
     return on;
+}
+
+// Tiles of at most four K blocks spend a large share of their time in the tile store: they get the
+// two-slab configuration (RF_FP8_GEMM_SHORTK=0 keeps the ordinary one).
+bool short_k_config(const GemmParams& p) {
+    static const bool on = [] {
+        const char* e = getenv("RF_FP8_GEMM_SHORTK");
+        return !(e && e[0] == '0');
+    }();
+    return on && p.splits == 1 && p.k <= 4 * BK;
 }
 
 template <class Cfg>
@@ -631,6 +657,9 @@ cudaError_t fp8_gemm_prepare_device() {
     e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg256::kSmemBytes);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256ShortK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg256ShortK::kSmemBytes);
+    if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(fp8_gemm_kernel<CfgPair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              CfgPair::kSmemBytes);
     if (e != cudaSuccess) return e;
@@ -654,8 +683,10 @@ cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, 
                         ? (block_n == 256 ? launch_cfg<Cfg256Mn>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
                                           : launch_cfg<Cfg128Mn>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream))
                     : block_n == 512 ? launch_cfg<CfgPair>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
-                    : block_n == 256 ? launch_cfg<Cfg256>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
-                                     : launch_cfg<Cfg128>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream);
+                    : block_n == 256
+                        ? (short_k_config(p) ? launch_cfg<Cfg256ShortK>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
+                                             : launch_cfg<Cfg256>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream))
+                        : launch_cfg<Cfg128>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream);
     if (e != cudaSuccess) return e;
     if (p.splits > 1) {
         const size_t mn = (size_t)p.m * p.n;

@@ -83,3 +83,28 @@ def test_registered_plan_is_used_and_correct(rf_lib, bn, split):
         assert ok, (n_bad, max_err)
     finally:
         rf_lib.rf_fp8_gemm_set_plan(m, n, k, 0, 0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(300, 576, 512), (1024, 320, 256), (129, 64, 128), (2048, 1088, 384)])
+def test_short_k_two_slab_configuration_with_ragged_tiles(rf_lib, m, n, k):
+    """K <= 512 with the 256-wide tile runs the configuration with two store slabs per warp; N values that leave
+    the last tile with one 64-column chunk (or a ragged one) exercise the slab alternation across tiles."""
+    import torch
+    from oracle import fp8_gemm as o
+    from radeonflow_kernels_b200 import gemm as G
+    from tests.helpers import canary_intact, canary_output, gemm_device_inputs
+    a, b, a_s, b_s = o.generate_input(m, n, k, 5 + m, "randn")
+    assert rf_lib.rf_fp8_gemm_set_plan(m, n, k, 256, 1) == 0
+    try:
+        da, db, das, dbs = gemm_device_inputs(a, b, a_s, b_s)
+        full, c = canary_output(m, n)
+        for _ in range(2):
+            G.fp8_mm(da, db, das, dbs, c)
+        torch.cuda.synchronize()
+        assert G.device_status() == 0
+        assert canary_intact(full, m, n)
+        ok, n_bad, max_err = o.check(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a, b, a_s, b_s))
+        assert ok, (n_bad, max_err)
+    finally:
+        rf_lib.rf_fp8_gemm_set_plan(m, n, k, 0, 0)
