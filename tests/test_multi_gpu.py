@@ -174,3 +174,46 @@ def test_multi_gpu_worker_all_visible_gpus():
     assert res.returncode == 0, out[-4000:]
     for r in range(n):
         assert f"MGPU OK rank={r}" in out, out[-4000:]
+
+
+def test_balanced_expert_placement_is_a_permutation_and_balances_skewed_load():
+    from radeonflow_kernels_b200.multi_gpu import balanced_expert_placement
+    rng = np.random.default_rng(3)
+    e, world = 256, 8
+    # skewed popularity with a random rank per expert; the hottest expert stays below one rank's fair share
+    # (top-k routing without replacement caps an expert at one pair per token), so a balanced placement exists
+    loads = 1.0 / (1.0 + rng.permutation(e)) ** 0.5
+    order = balanced_expert_placement(loads, world)
+    assert sorted(order.tolist()) == list(range(e))                    # every expert placed exactly once
+    per_rank = loads[order].reshape(world, e // world).sum(axis=1)
+    contiguous = loads.reshape(world, e // world).sum(axis=1)
+    assert per_rank.max() / per_rank.mean() < 1.05                     # near-perfect balance ...
+    assert contiguous.max() / contiguous.mean() > per_rank.max() / per_rank.mean()     # ... better than id order
+    # ties and equal loads: deterministic, still E/world experts per rank
+    order2 = balanced_expert_placement(np.ones(16), 4)
+    assert sorted(order2.tolist()) == list(range(16))
+    assert order2.tolist() == balanced_expert_placement(np.ones(16), 4).tolist()
+
+
+def test_layout_planner_matches_a_brute_force_statement():
+    """send_base / recv_offsets against a direct construction of every owner's receive buffer: rows ordered
+    by expert, then by source rank starting at the owner, then by the source's own order."""
+    from radeonflow_kernels_b200.multi_gpu import ep_layout_reference
+    rng = np.random.default_rng(11)
+    world, e = 4, 16
+    per = e // world
+    counts = rng.integers(0, 7, size=(world, e))
+    for q in range(world):                                             # build owner q's buffer explicitly
+        rows, offsets = [], [0]
+        for ex in range(q * per, (q + 1) * per):
+            for j in range(world):
+                s = (q + j) % world
+                rows += [(ex, s, i) for i in range(counts[s, ex])]
+            offsets.append(len(rows))
+        for s in range(world):
+            sb, ro = ep_layout_reference(counts, s)
+            for ex in range(q * per, (q + 1) * per):
+                if counts[s, ex]:
+                    assert rows[sb[ex]] == (ex, s, 0) and rows[sb[ex] + counts[s, ex] - 1] == (ex, s, counts[s, ex] - 1)
+            if s == q:
+                assert ro.tolist() == offsets
