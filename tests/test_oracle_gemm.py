@@ -105,3 +105,23 @@ def test_fnuz_oracle_is_quarter_of_fn_oracle_on_shared_bytes():
     fz = o.bf16_bits_to_f32(o.fp8_gemm_fnuz(a, b, a_s, b_s))
     fn = o.bf16_bits_to_f32(o.f32_to_bf16_bits(np.float32(0.25) * o.fp8_gemm_f32(a, b, a_s, b_s)))
     assert np.allclose(fz, fn, rtol=2 ** -7, atol=1e-6 * np.abs(fz).max())
+
+
+def test_fp8_codecs_round_trip_and_round_to_nearest():
+    """encode(decode(b)) == b for every finite byte of both formats, and encode picks a nearest value
+    (ties allowed either way at exact midpoints) for arbitrary inputs inside the format's range."""
+    for dec, enc, table, top in ((o.decode_e4m3fn, o.encode_e4m3fn, o.E4M3FN_TO_F32, 448.0),
+                                 (o.decode_e4m3fnuz, o.encode_e4m3fnuz, o.E4M3FNUZ_TO_F32, 240.0)):
+        bytes_ = np.arange(256, dtype=np.uint8)
+        vals = dec(bytes_)
+        finite = np.isfinite(vals)
+        back = enc(vals[finite])
+        # -0 has no byte of its own in fnuz (0x80 is NaN) and may come back as +0 in fn
+        assert np.array_equal(dec(back), vals[finite])
+        rng = np.random.default_rng(0)
+        x = np.concatenate([rng.uniform(-top, top, 20000), rng.standard_normal(20000),
+                            rng.uniform(-2.0 ** -6, 2.0 ** -6, 5000)]).astype(np.float32)
+        got = dec(enc(x)).astype(np.float64)
+        grid = np.unique(table[np.isfinite(table)].astype(np.float64))
+        nearest = np.abs(grid[None, :] - x.astype(np.float64)[:, None]).min(axis=1)
+        assert np.allclose(np.abs(got - x), nearest, rtol=0, atol=1e-12)
