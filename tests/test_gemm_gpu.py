@@ -129,6 +129,31 @@ def test_scale_linearity_and_zero_scale_full_size():
     assert_close(base[rows], exp)
 
 
+def test_largest_configuration_properties_and_spot_rows():
+    """M = 16384, N = 28672, K = 7168 (the multi-GPU configuration, here on one GPU): operands drawn on the
+    device, exact linearity in a power-of-two scale, and six full rows against the oracle."""
+    m, n, k = 16384, 28672, 7168
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev)
+    g.manual_seed(2024)
+    a = torch.randn((m, k), device=dev, generator=g).clamp_(-240, 240).to(torch.float8_e4m3fn)
+    b = torch.randn((n, k), device=dev, generator=g).clamp_(-240, 240).to(torch.float8_e4m3fn)
+    a_s = ((0.5 + 1.5 * torch.rand((m, k // 128), device=dev, generator=g)) * 2.0 ** -7).float()
+    b_s = ((0.5 + 1.5 * torch.rand((n // 128, k // 128), device=dev, generator=g)) * 2.0 ** -7).float()
+    c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    c2 = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    G.fp8_mm(a, b, a_s, b_s, c)
+    G.fp8_mm(a, b, a_s * 2, b_s, c2)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    assert torch.equal(c2.float(), 2 * c.float())
+    del c2
+    rows = torch.tensor([0, 127, 128, 8191, 12345, 16383], device=dev)
+    exp = o.fp8_gemm(a[rows].view(torch.uint8).cpu().numpy(), b.view(torch.uint8).cpu().numpy(),
+                     a_s[rows].cpu().numpy(), b_s.cpu().numpy())
+    assert_close(c[rows].view(torch.uint16).cpu().numpy(), exp)
+
+
 def test_extreme_fp8_values():
     m, n, k = 128, 128, 256
     rng = np.random.default_rng(8)
