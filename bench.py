@@ -15,6 +15,12 @@ max over ranks.
 
 `--impl reference` times the CPU restatement of the reference's PyTorch oracle on the host cores
 on a bounded sample of the same sweep.
+
+The JSON line's `extras` hold the other configurations: the single-GPU MoE layer, the expert-parallel MoE
+layer (all N ranks, strong scaling) and the N-split GEMM.  Development aids: `--workload moe` (single-GPU
+MoE layer alone), `--workload multi` (the `extras` alone, under torchrun for N > 1), `--ep-pull` (expert
+outputs pulled by the combine instead of pushed by the second expert GEMM), `--shapes MxNxK,...`,
+`--no-extras`, `--no-cpu-baseline`.
 """
 import argparse
 import ctypes
