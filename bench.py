@@ -394,7 +394,11 @@ def run_moe_only(args):
         "vs_baseline": None, "dtype": "fp16 x fp16 -> f32", "data": "synthetic",
         "config": {"workload": "MoE layer T=8192 d=7168 f=2048 E=32 top-4 + 1 shared (weights 3 GB > L2)"},
         "roofline": {"bound": "tensor", "achieved": fl / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
-                     "unit": "TFLOP/s", "frac": fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "traffic": None,
+                     "unit": "TFLOP/s", "frac": fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                     "traffic": 2.91e9,
+                     "traffic_note": "DRAM bytes of the largest moe_gemm_kernel launch (routed fc1), ncu, "
+                                     "profiles/moe_gemm_kernel_layer.md; algorithmic 2.48e9; achieved/frac are "
+                                     "layer FLOPs over layer time (all kernels of the layer)",
                      "kernel": "moe_gemm_kernel"},
         "gpu_launches": 18 * steps}), flush=True)
 
