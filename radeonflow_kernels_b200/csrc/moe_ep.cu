@@ -13,16 +13,6 @@ namespace rf {
 
 namespace {
 
-// Select one of the (at most 8) peer pointers without indexing the kernel-parameter struct
-// dynamically (which would force a copy of the struct into local memory).
-__device__ __forceinline__ void* pick_peer(const PeerPtrs& pp, int q) {
-    void* r = pp.p[0];
-#pragma unroll
-    for (int i = 1; i < 8; ++i)
-        if (q == i) r = pp.p[i];
-    return r;
-}
-
 __global__ void __launch_bounds__(1024)
 ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_experts, int* __restrict__ send_base,
                  int* __restrict__ recv_offsets) {

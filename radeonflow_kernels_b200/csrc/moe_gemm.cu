@@ -47,15 +47,6 @@ __device__ __forceinline__ float silu_fp16_rounded(float g) {
     return __half2float(__float2half_rn(s));
 }
 
-// One of the (at most 8) peer pointers, without indexing the kernel-parameter struct dynamically.
-__device__ __forceinline__ void* pick_peer(const PeerPtrs& pp, int q) {
-    void* r = pp.p[0];
-#pragma unroll
-    for (int i = 1; i < 8; ++i)
-        if (q == i) r = pp.p[i];
-    return r;
-}
-
 // Work item -> (row tile, column block).  Items walk one chunk (up to kMoeChunkTiles row tiles of one
 // group, built by tile_list_kernel) for one column block, then the next column block of the same chunk:
 // the CTAs running at the same time share that group's weight column block, and the chunk's A tiles stay

@@ -26,6 +26,17 @@ cudaError_t moe_tile_list_launch(const int* offsets, int n_groups, int* tile_gro
 struct PeerPtrs {
     void* p[8];
 };
+#ifdef __CUDACC__
+// One of the (at most 8) peer pointers, selected without indexing the kernel-parameter struct dynamically
+// (which would force a copy of the struct into local memory).
+__device__ __forceinline__ void* pick_peer(const PeerPtrs& pp, int q) {
+    void* r = pp.p[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+        if (q == i) r = pp.p[i];
+    return r;
+}
+#endif
 // counts_all [world][n_experts] (row s = pairs per global expert on source rank s).  Writes
 //   send_base[e]      row, inside the owner rank's receive buffer, of this rank's first pair for expert e
 //   recv_offsets[j]   j = 0..n_experts/world: row range of local expert j in this rank's receive buffer
