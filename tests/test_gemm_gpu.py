@@ -54,7 +54,9 @@ def assert_close(got_bits, exp_bits):
     assert ok, f"{nbad} of {got_bits.size} elements outside rtol={RTOL}/atol={ATOL}; max abs err {mx}"
 
 
-GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "gemm_*.npz")))
+_ALL_GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "gemm_*.npz")))
+GOLDEN = [p for p in _ALL_GOLDEN if "fnuz" not in os.path.basename(p)]
+GOLDEN_FNUZ = [p for p in _ALL_GOLDEN if "fnuz" in os.path.basename(p)]
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
@@ -294,3 +296,22 @@ def test_fnuz_entry_reports_bytes_it_cannot_read(rf_lib, bad, where):
     assert st == 0
     assert G.device_status() == 16          # recorded, and cleared by the read
     assert G.device_status() == 0
+
+
+@pytest.mark.parametrize("path", GOLDEN_FNUZ, ids=[os.path.basename(p) for p in GOLDEN_FNUZ])
+def test_fnuz_entry_against_reference_fixtures(rf_lib, path):
+    """The reference's own data path (e4m3fnuz bytes, [k][m] / [k][n] storage) through `rf_fp8_gemm_colmajor_fnuz`
+    against the output of the reference's unmodified ref_kernel."""
+    z = np.load(path)
+    a, b, a_s, b_s = z["a"], z["b"], z["a_scale"], z["b_scale"]
+    m, k = a.shape
+    n = b.shape[0]
+    from tests.helpers import to_dev
+    da, db = to_dev(np.ascontiguousarray(a.T)), to_dev(np.ascontiguousarray(b.T))
+    das, dbs = to_dev(np.ascontiguousarray(a_s.T)), to_dev(np.ascontiguousarray(b_s.T))
+    full, c = canary_output(m, n)
+    assert rf_lib.rf_fp8_gemm_colmajor_fnuz(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(), c.data_ptr(),
+                                            m, n, k, None, 0, None) == 0
+    torch.cuda.synchronize()
+    assert G.device_status() == 0 and canary_intact(full, m, n)
+    assert_close(c.view(torch.uint16).cpu().numpy(), z["c_bits"])

@@ -7,7 +7,9 @@ import pytest
 
 from oracle import fp8_gemm as o
 
-GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "gemm_*.npz")))
+_ALL = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "gemm_*.npz")))
+GOLDEN = [p for p in _ALL if "fnuz" not in os.path.basename(p)]          # e4m3fn bytes, K-major
+GOLDEN_FNUZ = [p for p in _ALL if "fnuz" in os.path.basename(p)]         # the reference's own e4m3fnuz data path
 
 
 def test_golden_files_present():
@@ -125,3 +127,18 @@ def test_fp8_codecs_round_trip_and_round_to_nearest():
         grid = np.unique(table[np.isfinite(table)].astype(np.float64))
         nearest = np.abs(grid[None, :] - x.astype(np.float64)[:, None]).min(axis=1)
         assert np.allclose(np.abs(got - x), nearest, rtol=0, atol=1e-12)
+
+
+@pytest.mark.parametrize("path", GOLDEN_FNUZ, ids=[os.path.basename(p) for p in GOLDEN_FNUZ])
+def test_fnuz_oracle_matches_reference_output(path):
+    """Fixtures made by the reference's own recipe (randn cast to float8_e4m3fnuz, transposed views) and its
+    unmodified ref_kernel pin the e4m3fnuz reading of the numpy oracle."""
+    z = np.load(path)
+    assert len(GOLDEN_FNUZ) >= 2
+    got = o.fp8_gemm_fnuz(z["a"], z["b"], z["a_scale"], z["b_scale"])
+    ok, nbad, _ = o.check(got, z["c_bits"], rtol=2e-2, atol=1e-3)
+    assert ok, f"{nbad} elements outside the reference tolerance"
+    g = o.bf16_bits_to_f32(got).astype(np.float64)
+    e = o.bf16_bits_to_f32(z["c_bits"]).astype(np.float64)
+    assert np.all(np.abs(g - e) <= np.abs(e) * 2.0 ** -7 + 1e-6 * np.abs(e).max())
+    assert (got != z["c_bits"]).mean() < 1e-3
