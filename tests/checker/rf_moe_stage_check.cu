@@ -7,8 +7,9 @@
 // seq_experts_index, permuted_rows, rev_permuted_rows - integer stages are exact here), then prints the
 // twelve PerfMetrics entries (src/moe/moe.cpp:350-364).  No libtorch: the CPU side is plain C++ with OpenMP.
 //
-//   rf_moe_stage_check [--lib PATH] [-c CASE] [-l] [--full]
+//   rf_moe_stage_check [--lib PATH] [-c CASE] [-l] [--full] [--dump DIR]
 //     -l       list the cases and exit (needs no GPU)
+//     --dump DIR  with -c N: write the case's inputs and CPU stage tensors to DIR and exit (needs no GPU)
 //     -c N     run only case N
 //     --full   the reference's own parameter sets (d_hidden 7168, d_expert 2048; minutes of CPU time)
 //   exit code = number of failing stage tensors (0 = all cases passed), 100 = set-up error.
@@ -353,6 +354,37 @@ int compare_int(const char* name, const std::vector<int>& got, const std::vector
     return bad ? 1 : 0;
 }
 
+// --dump DIR: inputs and CPU stage tensors of one case as raw little-endian files, so that another
+// restatement (the numpy oracle of the Python tests) can be compared with this one without a GPU.
+template <class T>
+bool dump_vec(const std::string& dir, const char* name, const std::vector<T>& v) {
+    const std::string path = dir + "/" + name + ".bin";
+    FILE* f = fopen(path.c_str(), "wb");
+    if (!f) return false;
+    const bool ok = fwrite(v.data(), sizeof(T), v.size(), f) == v.size();
+    fclose(f);
+    return ok;
+}
+
+int dump_case(const InputParams& q, const std::string& dir) {
+    const Layer L = make_layer(q);
+    const Stages s = reference_stages(L);
+    bool ok = dump_vec(dir, "x", L.x) && dump_vec(dir, "logits", L.logits) && dump_vec(dir, "shared_gate", L.shared_gate) &&
+              dump_vec(dir, "shared_up", L.shared_up) && dump_vec(dir, "shared_down", L.shared_down);
+    for (int e = 0; e < L.E && ok; ++e)
+        ok = dump_vec(dir, ("gate" + std::to_string(e)).c_str(), L.gate[e]) &&
+             dump_vec(dir, ("up" + std::to_string(e)).c_str(), L.up[e]) &&
+             dump_vec(dir, ("down" + std::to_string(e)).c_str(), L.down[e]);
+    ok = ok && dump_vec(dir, "seq_experts_index", s.seq_experts_index) && dump_vec(dir, "seq_experts_softmax", s.seq_experts_softmax) &&
+         dump_vec(dir, "source_rows", s.source_rows) && dump_vec(dir, "permuted_experts", s.permuted_experts) &&
+         dump_vec(dir, "permuted_rows", s.permuted_rows) && dump_vec(dir, "first_token_offset", s.first_token_offset) &&
+         dump_vec(dir, "rev_permuted_rows", s.rev_permuted_rows) && dump_vec(dir, "expanded_seq_softmax", s.expanded_seq_softmax) &&
+         dump_vec(dir, "expanded_fc1_output", s.expanded_fc1_output) && dump_vec(dir, "expanded_fc2_output", s.expanded_fc2_output) &&
+         dump_vec(dir, "shared_fc2_output", s.shared_fc2_output) && dump_vec(dir, "final_output", s.final_output);
+    if (!ok) fprintf(stderr, "cannot write into %s\n", dir.c_str());
+    return ok ? 0 : 100;
+}
+
 typedef int (*run_topk_t)(MoEInputRaw*, rf_stream_t, PerfMetrics*);
 typedef int (*status_t)(int*);
 
@@ -436,14 +468,16 @@ int main(int argc, char** argv) {
     std::string lib = getenv("RF_B200_LIB") ? getenv("RF_B200_LIB") : "radeonflow_kernels_b200/librf_b200.so";
     int only = -1;
     bool list = false, full = false;
+    std::string dump_dir;
     for (int i = 1; i < argc; ++i) {
         const std::string a = argv[i];
         if (a == "--lib" && i + 1 < argc) lib = argv[++i];
+        else if (a == "--dump" && i + 1 < argc) dump_dir = argv[++i];
         else if (a == "-c" && i + 1 < argc) only = atoi(argv[++i]);
         else if (a == "-l") list = true;
         else if (a == "--full") full = true;
         else {
-            fprintf(stderr, "usage: %s [--lib PATH] [-c CASE] [-l] [--full]\n", argv[0]);
+            fprintf(stderr, "usage: %s [--lib PATH] [-c CASE] [-l] [--full] [--dump DIR]\n", argv[0]);
             return 100;
         }
     }
@@ -455,6 +489,13 @@ int main(int argc, char** argv) {
                    cases[i].batch_size * cases[i].seq_len, cases[i].d_hidden, cases[i].d_expert,
                    cases[i].n_routed_experts, cases[i].n_experts_per_token, cases[i].n_shared_experts, cases[i].seed);
         return 0;
+    }
+    if (!dump_dir.empty()) {
+        if (only < 0 || only >= n_cases) {
+            fprintf(stderr, "--dump needs -c CASE\n");
+            return 100;
+        }
+        return dump_case(cases[only], dump_dir);
     }
     void* handle = dlopen(lib.c_str(), RTLD_NOW);
     if (!handle) {
