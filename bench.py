@@ -13,11 +13,15 @@ With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same swe
 (independent GEMMs: replicas only, weak scaling, no data-path collective); the step time is the
 max over ranks.
 
-`--impl reference` times the CPU restatement of the reference's PyTorch oracle on the host cores
-on a bounded sample of the same sweep.
+`--impl reference` times the reference project's own PyTorch implementation of the path (`ref_kernel`,
+scripts/problems/gemm/reference.py:40-85, unmodified, from oracle/_ref) on the host cores with every
+thread the process may use, one pass over the same 18 shapes per step; where oracle/_ref is absent the
+numpy restatement of it stands in and the line says so (`cpu_baseline.kind`).
 
 The JSON line's `extras` hold the other configurations: the single-GPU MoE layer, the expert-parallel MoE
-layer (all N ranks, strong scaling) and the N-split GEMM.  Development aids: `--workload moe` (single-GPU
+layer (all N ranks, strong scaling) and the N-split GEMM; the two sharded ones carry a `parity` block (every
+rank checks rows of its result against the CPU oracle after the timed loop) and the run fails if one
+misses.  Development aids: `--workload moe` (single-GPU
 MoE layer alone), `--workload multi` (the `extras` alone, under torchrun for N > 1), `--ep-pull` (expert
 outputs pulled by the combine instead of pushed by the second expert GEMM), `--shapes MxNxK,...`,
 `--no-extras`, `--no-cpu-baseline`.
@@ -40,12 +44,13 @@ import numpy as np  # noqa: E402
 NK_PAIRS = [(1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
             (512, 7168), (4096, 512)]
 SWEEP = [(m, n, k) for m in (1024, 6144) for (n, k) in NK_PAIRS]
-CPU_SAMPLE = [(1024, n, k) for (n, k) in NK_PAIRS]      # the M=1024 half: ~190 GFLOP per pass
 # dram__bytes_read.sum + dram__bytes_write.sum of fp8_gemm_kernel for each sweep shape, in SWEEP order, from one
-# ncu pass over the first sweep of `bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-extras`
-# (profiles/fp8_gemm_kernel_sweep.md, section 3).  C mostly stays in the 126 MB L2, hence traffic < algorithmic.
+# ncu pass (two DRAM counters, --clock-control none) over a sweep of `bench.py --steps 2 --warmup 3
+# --no-cpu-baseline --no-extras`.  C mostly stays in the 126 MB L2, hence traffic < algorithmic.
 NCU_DRAM_BYTES = [18623744, 6396672, 11739904, 2159104, 16898048, 40659712, 19004416, 11280640, 2690816,
                   56950272, 14554880, 49672704, 30538752, 60639232, 114914816, 65986304, 49144320, 5449984]
+# same two counters for the largest moe_gemm_kernel launch of the single-GPU MoE layer (routed fc1)
+MOE_NCU_DRAM_BYTES = 2.91e9
 METRIC = "fp8_blockscaled_gemm_tflops"
 UNIT = "TFLOP/s"
 
@@ -149,62 +154,120 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------- CPU reference --
-def cpu_pass(problems):
-    """One pass of the CPU oracle over `problems`; returns (seconds, flops)."""
-    from oracle import fp8_gemm as o
-    t0 = time.perf_counter()
-    fl = 0.0
-    for (a, b, a_s, b_s) in problems:
-        o.fp8_gemm(a, b, a_s, b_s)
-        fl += gemm_flops(a.shape[0], b.shape[0], a.shape[1])
-    return time.perf_counter() - t0, fl
+def sweep_config(world, shapes_arg=""):
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": ("fp8 block-scaled GEMM, 18-shape sweep M in {1024,6144} x 9 (N,K)"
+                         if not shapes_arg else "fp8 block-scaled GEMM, restricted to " + shapes_arg),
+            "l2": "inputs larger than L2: one step touches ~1.0 GB; per-shape table rotates operand sets > L2",
+            "launch": "one CUDA graph replay per step",
+            "parallelism": "replicas" if world > 1 else "single"}
 
 
-def cpu_threads():
+def host_threads():
+    """Threads this process may use: every core of its affinity mask.  torchrun exports OMP_NUM_THREADS=1 to its
+    workers, so the CPU arm sets its thread count itself instead of inheriting it."""
     try:
-        from threadpoolctl import threadpool_info
-        n = [i.get("num_threads", 1) for i in threadpool_info() if i.get("user_api") == "blas"]
-        if n:
-            return max(n)
-    except Exception:
-        pass
-    return os.cpu_count() or 1
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
-def cpu_problems():
-    from oracle import fp8_gemm as o
-    return [o.generate_input(m, n, k, 100 + i, "baseline") for i, (m, n, k) in enumerate(CPU_SAMPLE)]
+def load_reference_module():
+    """The reference's scripts/problems/gemm/reference.py from oracle/_ref (written there by oracle/make_ref.py),
+    imported the way scripts/eval.py:157-169 imports it.  None when the copy is not there."""
+    base = os.path.join(ROOT, "oracle", "_ref", "scripts")
+    prob = os.path.join(base, "problems", "gemm")
+    if not os.path.exists(os.path.join(prob, "reference.py")) or not os.path.exists(os.path.join(base, "utils.py")):
+        return None
+    import importlib.util
+    saved = list(sys.path)
+    sys.path[:0] = [prob, base]
+    try:
+        spec = importlib.util.spec_from_file_location("task", os.path.join(prob, "task.py"))
+        task = importlib.util.module_from_spec(spec)
+        sys.modules["task"] = task
+        spec.loader.exec_module(task)
+        spec = importlib.util.spec_from_file_location("rf_reference_gemm", os.path.join(prob, "reference.py"))
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+        return ref
+    except Exception as e:                                  # an unreadable copy: say so and use the restatement
+        print(f"bench.py: oracle/_ref could not be imported ({e}); using the numpy restatement", file=sys.stderr)
+        return None
+    finally:
+        sys.path[:] = saved
+
+
+class CpuArm:
+    """The path on the host cores: the reference's own `ref_kernel` on CPU tensors (kind "reference") or, when
+    oracle/_ref is absent, the numpy restatement of it (kind "port").  Same data recipe as the GPU arm."""
+
+    def __init__(self, shapes):
+        import torch
+        from oracle import fp8_gemm as o
+        self.threads = host_threads()
+        torch.set_num_threads(self.threads)
+        self.ref = load_reference_module()
+        self.kind = "reference" if self.ref is not None else "port"
+        self.shapes = list(shapes)
+        self.problems = []
+        for i, (m, n, k) in enumerate(self.shapes):
+            a, b, a_s, b_s = o.generate_input(m, n, k, 100 + i, "baseline")
+            if self.ref is not None:
+                self.problems.append((torch.from_numpy(a).view(torch.float8_e4m3fn),
+                                      torch.from_numpy(b).view(torch.float8_e4m3fn), torch.from_numpy(a_s),
+                                      torch.from_numpy(b_s), torch.zeros((m, n), dtype=torch.bfloat16)))
+            else:
+                self.problems.append((a, b, a_s, b_s))
+        self.flops = sum(gemm_flops(*x) for x in self.shapes)
+
+    def one_pass(self, problems=None):
+        """Seconds of one pass over the problems."""
+        probs = self.problems if problems is None else problems
+        t0 = time.perf_counter()
+        if self.ref is not None:
+            import torch
+            with torch.no_grad():
+                for data in probs:
+                    self.ref.ref_kernel(data)
+        else:
+            from oracle import fp8_gemm as o
+            from threadpoolctl import threadpool_limits
+            with threadpool_limits(limits=self.threads):
+                for (a, b, a_s, b_s) in probs:
+                    o.fp8_gemm(a, b, a_s, b_s)
+        return time.perf_counter() - t0
+
+    def describe(self, passes, seconds):
+        what = ("the reference's ref_kernel (scripts/problems/gemm/reference.py:40-85, unmodified, torch CPU)"
+                if self.ref is not None else "numpy restatement of the reference's ref_kernel (oracle/_ref absent)")
+        return (f"{passes} pass(es) of {what} over the {len(self.shapes)} shapes of the sweep "
+                f"({self.flops / 1e9:.0f} GFLOP per pass, {seconds:.1f} s)")
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    probs = cpu_problems()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    arm = CpuArm(SWEEP)
     for _ in range(max(1, min(args.warmup, 1))):
-        cpu_pass(probs[:2])
-    times = []
-    fl = 0.0
+        arm.one_pass(arm.problems[:2])
     steps = max(1, args.steps)
-    for _ in range(steps):
-        t, fl = cpu_pass(probs)
-        times.append(t)
+    times = [arm.one_pass() for _ in range(steps)]
     tsum = sum(times)
-    val = fl * steps / tsum / 1e12
-    cores = cpu_threads()
-    sample = "numpy port of the reference oracle (dequantise, fp32 matmul, bf16) on the 9 M=1024 shapes of the sweep"
+    val = arm.flops * steps / tsum / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": args.warmup, "ms_per_step": tsum / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 (CPU dequantised e4m3)", "data": "synthetic",
-        "config": {"workload": "fp8 block-scaled GEMM 18-shape sweep; CPU arm times its M=1024 half per step",
-                   "shapes": CPU_SAMPLE},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": sweep_config(world, args.shapes),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": arm.threads, "kind": arm.kind,
+                         "sample": arm.describe(steps, tsum)},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
-
 
 
 # ------------------------------------------------------------------------- extra workloads --
@@ -254,6 +317,119 @@ def make_moe_weights(torch, dev, d, f, experts, seed, with_router_for=None):
     return w
 
 
+def measure_fp8_peak(torch, dev):
+    """Yardstick only: a plain (unscaled-block) FP8 GEMM of the vendor library, e4m3 8192^3 through
+    torch._scaled_mm, best of 10 after warm-up, in TFLOP/s.  None when the call is not available."""
+    try:
+        n = 8192
+        a = torch.randn((n, n), device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn((n, n), device=dev).to(torch.float8_e4m3fn).t()      # column-major second operand
+        one = torch.ones((), device=dev)
+        f = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            f()
+        torch.cuda.synchronize()
+        best = 0.0
+        for _ in range(10):
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            best = max(best, 2.0 * n ** 3 / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        return best
+    except Exception as e:
+        print(f"bench.py: FP8 yardstick GEMM unavailable ({e})", file=sys.stderr)
+        return None
+
+
+def _all_ranks_ok(ok, dev, world, dist):
+    import torch
+    t = torch.tensor([1.0 if ok else 0.0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item() > 0.5)
+
+
+def check_nsplit_parity(torch, dist, dev, rank, world, a, a_s, c_full, m, n, kk, shard_seed):
+    """Every rank: six full rows of its assembled C against the CPU oracle (every rank's B shard is regenerated
+    from its seed), and a checksum of C that must agree on all ranks."""
+    from oracle import fp8_gemm as og
+    n_loc = n // world
+    rows = [0, 1, m // 3, m // 2 + 5, m - 2, m - 1]
+    ridx = torch.tensor(rows, device=dev)
+    a_rows = a[ridx].view(torch.uint8).cpu().numpy()
+    as_rows = a_s[ridx].cpu().numpy()
+    got = c_full[ridx].view(torch.uint16).cpu().numpy()
+    g = torch.Generator(device=dev)
+    worst, bad = 0.0, 0
+    for r in range(world):
+        g.manual_seed(shard_seed + r)
+        b_r = torch.randn((n_loc, kk), device=dev, generator=g).clamp_(-240, 240).to(torch.float8_e4m3fn)
+        bs_r = ((0.5 + 1.5 * torch.rand((n_loc // 128, kk // 128), device=dev, generator=g)) * 2.0 ** -7).float()
+        exp = og.fp8_gemm(a_rows, b_r.view(torch.uint8).cpu().numpy(), as_rows, bs_r.cpu().numpy())
+        ok, nbad, mx = og.check(got[:, r * n_loc:(r + 1) * n_loc], exp)
+        bad += int(nbad)
+        worst = max(worst, float(mx))
+        del b_r, bs_r
+    # the same bytes everywhere: sum of C read as int16 (exact in int64), max and min over ranks must agree
+    cs = c_full.view(torch.int16).to(torch.int64).sum().reshape(1)
+    hi, lo = cs.clone(), cs.clone()
+    if world > 1:
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    same = bool((hi == lo).item())
+    ok = _all_ranks_ok(bad == 0 and same, dev, world, dist)
+    return {"ok": ok, "rows_checked_per_rank": len(rows), "elements_out_of_tolerance_rank0": bad,
+            "max_abs_err_rank0": worst, "checksum_equal_on_all_ranks": same,
+            "oracle": "oracle.fp8_gemm (restatement of scripts/problems/gemm/reference.py:40-87), rtol 2e-2 atol 1e-3"}
+
+
+def check_ep_parity(torch, dist, dev, rank, world, layer, x, out, router_w_placed, bias_placed, order, d, f, e, k,
+                    weight_seed):
+    """Every rank: four of its tokens against the CPU oracle restricted to those tokens' experts.  Expert
+    weights are seeded per ORIGINAL expert id, so any rank regenerates the few it needs; `order` maps a placed
+    (renumbered) expert id to the original one."""
+    from oracle import moe as om
+    t_loc = x.shape[0]
+    toks = [0, t_loc // 3, (2 * t_loc) // 3 + 1, t_loc - 1]
+    tidx = torch.tensor(toks, device=dev)
+    x_rows = x[tidx].cpu().numpy()
+    logits_dev = layer.scores[tidx].cpu().numpy()
+    idx_dev = layer.idx[tidx].cpu().numpy()
+    out_dev = out[tidx].cpu().numpy()
+    # router logits within tolerance of the oracle's; the top-k rule is then applied to the DEVICE logits
+    ref_logits = om.router_logits(x_rows, router_w_placed.cpu().numpy(), bias_placed)
+    ok_l, nb_l, mx_l = om.check(logits_dev, ref_logits)
+    idx_ref, w_ref, _ = om.route(logits_dev, k)
+    idx_exact = bool(np.array_equal(idx_ref, idx_dev))
+    g = torch.Generator(device=dev)
+    g.manual_seed(weight_seed)
+    torch.randn((e, d), device=dev, generator=g)                   # the router draw precedes the shared expert's
+    sh = [(torch.randn(shape, device=dev, generator=g) / sc ** 0.5).half().cpu().numpy()
+          for shape, sc in (((d, f), f), ((d, f), f), ((f, d), d))]
+    acc = om.linear_fp16(om.swiglu_fc1(x_rows, sh[0], sh[1]), sh[2]).astype(np.float32)
+    cache = {}
+    for ti in range(len(toks)):
+        for j in range(k):
+            orig = int(order[int(idx_ref[ti, j])])
+            if orig not in cache:
+                g.manual_seed(weight_seed * 1000 + orig)
+                cache[orig] = [(torch.randn(shape, device=dev, generator=g) / sc ** 0.5).half().cpu().numpy()
+                               for shape, sc in (((d, f), f), ((d, f), f), ((f, d), d))]
+            wg, wu, wd = cache[orig]
+            y = om.linear_fp16(om.swiglu_fc1(x_rows[ti:ti + 1], wg, wu), wd).astype(np.float32)
+            acc[ti] += np.float32(w_ref[ti, j]) * y[0]
+    ok_o, nb_o, mx_o = om.check(out_dev, acc.astype(np.float16))
+    ok = _all_ranks_ok(bool(ok_l) and idx_exact and bool(ok_o), dev, world, dist)
+    return {"ok": ok, "tokens_checked_per_rank": len(toks), "indices_exact_rank0": idx_exact,
+            "logits_out_of_tolerance_rank0": int(nb_l), "output_out_of_tolerance_rank0": int(nb_o),
+            "max_abs_err_rank0": float(mx_o),
+            "oracle": "oracle.moe (restatement of scripts/problems/moe/reference.py:72-101), rtol 1e-2 atol 1e-2, "
+                      "top-k indices exact on the device's logits"}
+
+
 def run_extras(args, rank, world, dev, dist, peaks):
     """MoE layer tokens/s (single-GPU config and the expert-parallel config) and the N-split GEMM."""
     import torch
@@ -277,7 +453,15 @@ def run_extras(args, rank, world, dev, dist, peaks):
     out["moe_single_gpu"] = {
         "config": "T=8192 d=7168 f=2048 E=32 top-4 + 1 shared, fp16, router GEMM included",
         "ms_per_layer": ms, "tokens_per_s": world * t / (ms * 1e-3), "tflops_per_gpu": fl / (ms * 1e-3) / 1e12,
-        "frac_f16_peak": fl / (ms * 1e-3) / 1e12 / f16_peak, "parallelism": "replicas" if world > 1 else "single"}
+        "frac_f16_peak": fl / (ms * 1e-3) / 1e12 / f16_peak, "parallelism": "replicas" if world > 1 else "single",
+        "roofline": {"bound": "tensor", "achieved": fl / (ms * 1e-3) / 1e12, "peak": f16_peak, "unit": "TFLOP/s",
+                     "frac": fl / (ms * 1e-3) / 1e12 / f16_peak,
+                     "frac_of_sustained_peak": fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                     "kernel": "moe_gemm_kernel", "traffic": MOE_NCU_DRAM_BYTES,
+                     "traffic_note": "DRAM bytes of the largest moe_gemm_kernel launch of the layer (routed fc1), ncu; "
+                                     "algorithmic 2.48e9; achieved is layer FLOPs over layer time (all kernels)",
+                     "peak_source": f"bf16_tflops of {peaks['source']} (the layer runs for milliseconds at the power "
+                                    "cap: the sustained figure is the fairer one)"}}
     del buf, w, x
     torch.cuda.empty_cache()
 
@@ -285,11 +469,13 @@ def run_extras(args, rank, world, dev, dist, peaks):
     d, f, e, k, t_total = 7168, 2048, 256, 8, 32768
     t_loc = t_total // world
     e_loc = e // world
-    # Static load-aware placement decided before the timed region: one calibration pass of the router
-    # and top-k kernels over this run's tokens gives pairs per expert; experts are then renumbered in
-    # placement order (router rows and bias permuted), which leaves the layer itself unchanged.
+    # Static load-aware placement decided before the timed region from a CALIBRATION batch drawn with another
+    # seed than the timed batch: the router and top-k kernels give pairs per expert; experts are then renumbered
+    # in placement order (router rows and bias permuted), which leaves the layer itself unchanged.
     # load skew: logit bias -1.1 * ln(1 + rank_e) with a seeded random rank per expert (Zipf(1.1) popularity)
     bias_np = (-1.1 * np.log1p(np.random.default_rng(17).permutation(e).astype(np.float64))).astype(np.float32)
+    g.manual_seed(900 + rank)
+    x_cal = torch.randn((t_loc, d), device=dev, dtype=torch.float16, generator=g)
     g.manual_seed(100 + rank)
     x = torch.randn((t_loc, d), device=dev, dtype=torch.float16, generator=g)
     g.manual_seed(13)
@@ -299,12 +485,14 @@ def run_extras(args, rank, world, dev, dist, peaks):
     cal_w = torch.empty((t_loc, k), dtype=torch.float16, device=dev)
     cal_src = torch.empty((t_loc * k,), dtype=torch.int32, device=dev)
     bias0 = torch.from_numpy(bias_np).to(dev)
-    L.rf_moe_router_gemm(x.data_ptr(), router_w.data_ptr(), bias0.data_ptr(), t_loc, e, d, cal_scores.data_ptr(), sp)
+    L.rf_moe_router_gemm(x_cal.data_ptr(), router_w.data_ptr(), bias0.data_ptr(), t_loc, e, d, cal_scores.data_ptr(),
+                         sp)
     L.rf_moe_topk(cal_scores.data_ptr(), t_loc, e, k, cal_idx.data_ptr(), cal_w.data_ptr(), cal_src.data_ptr(), sp)
     loads = torch.bincount(cal_idx.reshape(-1).long(), minlength=e).double()
     if world > 1:
         dist.all_reduce(loads)
     order = mg.balanced_expert_placement(loads.cpu().numpy(), world)
+    del x_cal, cal_scores, cal_idx, cal_w, cal_src
     w = make_moe_weights(torch, dev, d, f, [int(order[rank * e_loc + j]) for j in range(e_loc)], 13,
                          with_router_for=e)
     w["router.weight"] = router_w[torch.from_numpy(order).to(dev)].contiguous()
@@ -312,28 +500,47 @@ def run_extras(args, rank, world, dev, dist, peaks):
            "batch_size": 1, "seq_len": t_loc}
     bias = torch.from_numpy(bias_np[order]).to(dev)
     layer = mg.ExpertParallelMoE(cfg, w, t_loc, dev, router_bias=bias, push_results=not args.ep_pull)
+    if args.ep_dispatch_blocks:
+        layer.set_dispatch_blocks(args.ep_dispatch_blocks)
     ms = _timed(lambda: layer.forward(x), 5, 2, dev, world, dist)
-    layer.trace = []
-    layer.forward(x)
+    layer.set_trace(True)
+    y = layer.forward(x)
     stages = {name: round(ms_, 4) for name, ms_ in layer.stage_times_ms()}
-    layer.trace = None
+    layer.set_trace(False)
     rows = torch.tensor([float(layer.received_rows())], dtype=torch.float64, device=dev)
     mx, sm = rows.clone(), rows.clone()
     if world > 1:
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    parity = check_ep_parity(torch, dist, dev, rank, world, layer, x, y, w["router.weight"], bias_np[order], order, d,
+                             f, e, k, 13)
+    status = ctypes.c_int(0)
+    L.rf_device_status(ctypes.byref(status))
+    parity["device_status"] = status.value
+    parity["ok"] = parity["ok"] and _all_ranks_ok(status.value == 0, dev, world, dist)
     fl = moe_layer_flops(t_total, d, f, e, k)
+    peak_total = world * peaks["bf16_tflops_sustained"]
+    nv = (world - 1) / world * t_loc * k * d * 2            # bytes each GPU sends (and receives) per direction
+    bound_ms = max(fl / (peak_total * 1e12), 2 * nv / 770e9) * 1e3
     out["moe_expert_parallel"] = {
         "config": "32768 tokens, d=7168 f=2048 E=256 top-8 + 1 shared, Zipf(1.1) router bias; experts sharded E/N "
-                  "per GPU by a static load-aware placement from one calibration pass; dispatch by peer stores, "
+                  "per GPU by a static load-aware placement from a calibration batch drawn with another seed; "
+                  "dispatch by peer stores, "
                   + ("combine by peer loads" if (args.ep_pull or world == 1) else
                      "expert outputs pushed home by the second GEMM's epilogue (peer stores), local combine"),
         "ms_per_layer": ms, "tokens_per_s": t_total / (ms * 1e-3), "tflops_total": fl / (ms * 1e-3) / 1e12,
         "stage_ms_rank0": stages, "scaling": "strong", "rows_per_gpu_max": mx.item(), "rows_per_gpu_mean": sm.item() / world,
-        "imbalance_max_over_mean": mx.item() / (sm.item() / world)}
+        "imbalance_max_over_mean": mx.item() / (sm.item() / world), "parity": parity,
+        "roofline": {"bound": "tensor", "achieved": fl / (ms * 1e-3) / 1e12, "peak": peak_total, "unit": "TFLOP/s",
+                     "frac": fl / (ms * 1e-3) / 1e12 / peak_total, "kernel": "moe_gemm_kernel", "traffic": None,
+                     "target_ms": bound_ms,
+                     "peak_source": f"N x bf16_tflops_sustained of {peaks['source']}; target_ms = max(FLOPs / that, "
+                                    "dispatch + return bytes per GPU / 770 GB/s measured peer bandwidth)"}}
     layer.close()
-    del layer, w, x
+    del layer, w, x, y
     torch.cuda.empty_cache()
+    if not parity["ok"]:
+        raise SystemExit(f"bench.py: expert-parallel MoE parity failed on {world} GPU(s): {json.dumps(parity)}")
 
     # ---- config 2: M=16384 N=28672 K=7168 split along N, C assembled on every GPU by the epilogue
     m, n, kk = 16384, 28672, 7168
@@ -351,18 +558,28 @@ def run_extras(args, rank, world, dev, dist, peaks):
         mg.fp8_gemm_nsplit(a, b, a_s, b_s, cbuf, m, n, kk)
         mg.stream_barrier(flag)
     ms = _timed(step, 5, 2, dev, world, dist)
+    parity = check_nsplit_parity(torch, dist, dev, rank, world, a, a_s, cbuf.tensor(torch.bfloat16, (m, n)), m, n, kk,
+                                 70)
     c_loc = torch.empty((m, n_loc), dtype=torch.bfloat16, device=dev)
     ms_local = _timed(lambda: L.rf_fp8_gemm(a.data_ptr(), b.data_ptr(), a_s.data_ptr(), b_s.data_ptr(),
                                             c_loc.data_ptr(), m, n_loc, kk, 1, None, 0, sp), 5, 2, dev, world, dist)
     fl = 2.0 * m * n * kk
     nv_bytes = (world - 1) / world * m * n * 2          # C bytes each GPU receives over NVLink
+    fp8_peak = peaks.get("fp8_tflops") or 2 * peaks["bf16_tflops"]
+    roof_ms = max(fl / world / (fp8_peak * 1e12), nv_bytes / 770e9) * 1e3
     out["gemm_nsplit"] = {
         "config": "M=16384 N=28672 K=7168 fp8, B row-partitioned, bf16 C all-gathered by epilogue peer stores",
         "ms": ms, "tflops_total": fl / (ms * 1e-3) / 1e12, "ms_gemm_only_local_c": ms_local,
         "tflops_total_gemm_only": fl / (ms_local * 1e-3) / 1e12, "scaling": "strong",
-        "nvlink_bytes_in_per_gpu": nv_bytes,
-        "roofline_ms": max(fl / world / (2 * peaks["bf16_tflops"] * 1e12), nv_bytes / 770e9) * 1e3}
+        "nvlink_bytes_in_per_gpu": nv_bytes, "roofline_ms": roof_ms, "parity": parity,
+        "roofline": {"bound": "tensor" if fl / world / (fp8_peak * 1e12) > nv_bytes / 770e9 else "nvlink",
+                     "achieved": roof_ms / ms, "peak": 1.0, "unit": "fraction of the target time", "frac": roof_ms / ms,
+                     "kernel": "fp8_gemm_kernel", "traffic": None,
+                     "peak_source": "target time = max(FLOPs per GPU / FP8 peak of this run, C bytes received per GPU "
+                                    "/ 770 GB/s measured peer bandwidth)"}}
     cbuf.close()
+    if not parity["ok"]:
+        raise SystemExit(f"bench.py: N-split GEMM parity failed on {world} GPU(s): {json.dumps(parity)}")
     return out
 
 
@@ -395,10 +612,10 @@ def run_moe_only(args):
         "config": {"workload": "MoE layer T=8192 d=7168 f=2048 E=32 top-4 + 1 shared (weights 3 GB > L2)"},
         "roofline": {"bound": "tensor", "achieved": fl / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
-                     "traffic": 2.91e9,
-                     "traffic_note": "DRAM bytes of the largest moe_gemm_kernel launch (routed fc1), ncu, "
-                                     "profiles/moe_gemm_kernel_layer.md; algorithmic 2.48e9; achieved/frac are "
-                                     "layer FLOPs over layer time (all kernels of the layer)",
+                     "traffic": MOE_NCU_DRAM_BYTES,
+                     "traffic_note": "DRAM bytes of the largest moe_gemm_kernel launch (routed fc1), ncu capture; "
+                                     "algorithmic 2.48e9; achieved/frac are layer FLOPs over layer time (all "
+                                     "kernels of the layer)",
                      "kernel": "moe_gemm_kernel"},
         "gpu_launches": 18 * steps}), flush=True)
 
@@ -527,7 +744,12 @@ def run_gpu_arm(args):
     # ---- per-shape table: each shape alone, as a graph of R launches that rotate over R operand sets
     # whose total footprint exceeds L2 (so every launch reads its operands from HBM)
     peaks = measured_peaks()
-    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    # FP8 tensor peak: measured in this run with a plain vendor-library FP8 GEMM (a yardstick, not part of the
+    # path); 2 x the measured bf16 figure only if that call is unavailable
+    fp8_measured = measure_fp8_peak(torch, dev)
+    fp8_assumed = 2.0 * peaks["bf16_tflops"]
+    fp8_peak = fp8_measured if fp8_measured else fp8_assumed
+    peaks["fp8_tflops"] = fp8_peak
     per_shape = []
     for s in shapes:
         m, n, k = s["m"], s["n"], s["k"]
@@ -561,6 +783,8 @@ def run_gpu_arm(args):
             "m": m, "n": n, "k": k, "split_k": s["split"], "us": round(us, 2),
             "tflops": round(fl / us / 1e6, 1), "frac_fp8_peak": round(fl / us / 1e6 / fp8_peak, 3),
             "gbs": round(by / us / 1e3, 1), "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 3),
+            # the shape's own bound: the slower of its tensor time and its HBM time, over the measured time
+            "frac_of_bound": round(max(fl / (fp8_peak * 1e6), by / (peaks["hbm_gbs"] * 1e3)) / us, 3),
             "rotating_sets": reps,
         })
         del sets, g2
@@ -630,35 +854,34 @@ def run_gpu_arm(args):
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            probs = cpu_problems()
-            cpu_pass(probs[:1])
-            tsec, fl = cpu_pass(probs)
-            reps = 1
-            while tsec < 10.0 and reps < 20:
-                t_more, _ = cpu_pass(probs)
-                tsec += t_more
+            # bounded sample of the same workload on the host cores: whole passes over the 18 shapes until
+            # about 12 s of CPU work have been timed (at least two passes after one warm-up of two shapes)
+            arm = CpuArm(SWEEP)
+            arm.one_pass(arm.problems[:2])
+            tsec, reps = 0.0, 0
+            while reps < 2 or (tsec < 12.0 and reps < 20):
+                tsec += arm.one_pass()
                 reps += 1
-            cpu = {"value": fl * reps / tsec / 1e12, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
-                   "sample": f"{reps} pass(es) of the numpy oracle over the 9 M=1024 shapes of the sweep "
-                             f"({fl / 1e9:.0f} GFLOP per pass, {tsec:.1f} s)"}
+            cpu = {"value": arm.flops * reps / tsec / 1e12, "unit": UNIT, "cores": arm.threads, "kind": arm.kind,
+                   "sample": arm.describe(reps, tsec)}
         achieved = step_flops / (ms_step * 1e-3) / 1e12
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8 e4m3 x e4m3 -> f32 (exact f32 block scales), bf16 out",
             "data": "synthetic",
-            "config": {"workload": ("fp8 block-scaled GEMM, 18-shape sweep M in {1024,6144} x 9 (N,K)"
-                                    if not args.shapes else "fp8 block-scaled GEMM, restricted to " + args.shapes),
-                       "l2": "inputs larger than L2: one step touches ~1.0 GB; per-shape table rotates operand sets > L2",
-                       "launch": "one CUDA graph replay per step",
-                       "parallelism": "replicas" if world > 1 else "single"},
+            "config": sweep_config(world, args.shapes),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": achieved / fp8_peak,
-                         "frac_of_sustained_peak": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
+                         "frac_of_2x_bf16_burst": achieved / fp8_assumed,
+                         "frac_of_2x_bf16_sustained": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
                          "traffic": (sum(NCU_DRAM_BYTES) / len(NCU_DRAM_BYTES) if not args.shapes else None),
                          "traffic_note": "DRAM bytes per fp8_gemm_kernel launch, mean over the 18 shapes, ncu; "
                                          f"algorithmic mean {sum(gemm_bytes(*x) for x in SWEEP) / len(SWEEP):.0f}",
-                         "peak_source": f"2 x bf16_tflops of {peaks['source']} (fp8 rate = 2 x bf16)",
+                         "peak_source": ("plain FP8 GEMM of the vendor library (torch._scaled_mm, e4m3 8192^3, best of 10) "
+                                         "measured in this run as a yardstick" if fp8_measured else
+                                         f"2 x bf16_tflops of {peaks['source']} (FP8 yardstick GEMM unavailable)"),
+                         "peak_2x_bf16_burst": fp8_assumed,
                          "kernel": "fp8_gemm_kernel"},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -681,6 +904,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE and N-split GEMM workloads")
+    ap.add_argument("--ep-dispatch-blocks", type=int, default=0,
+                    help="expert-parallel MoE: grid cap of the dispatch kernel (0 = library default)")
     ap.add_argument("--ep-pull", action="store_true",
                     help="expert-parallel MoE: combine pulls the expert outputs instead of fc2 pushing them")
     ap.add_argument("--workload", default="sweep", choices=["sweep", "moe", "multi"],

@@ -106,10 +106,17 @@ int rf_fp8_gemm_colmajor(const void *a, const void *b, const float *as, const fl
 /* rf_fp8_gemm_colmajor for operands whose bytes are e4m3fnuz (bias 8, the MI300X format the reference
  * computes in: __hip_fp8_e4m3_fnuz, src/gemm/gemm_kernel.cpp:30-34; tests/checker/checker.cpp casts to
  * torch.float8_e4m3fnuz).  A fnuz byte read as OCP e4m3fn is exactly twice its value, subnormals included,
- * so the tensor cores consume the bytes unchanged and the epilogue multiplies the fp32 tile by 1/4 (exact).
- * Three fnuz bytes have no counterpart under that reading: 0x80 (NaN), 0x7F and 0xFF (+-240).  Both
- * operands are scanned on the stream before the GEMM; if one is found the GEMM still runs, and the next
- * rf_device_status() returns RF_ERR_DEVICE_TIMEOUT with detail 16.  m*k and n*k must be multiples of 16. */
+ * so the tensor cores consume the bytes unchanged and the epilogue folds 1/2 per operand into the scale
+ * product (exact).  Three fnuz bytes have no counterpart under that reading: 0x80 (NaN), 0x7F and 0xFF
+ * (+-240, which amax-scaled quantisation puts into practically every 128-block).  One pass per operand
+ * ahead of the GEMM writes the e4m3fn bytes of EQUAL value into library-owned scratch (m*k + n*k bytes,
+ * grown on first use) and flags an operand that holds one of the three bytes; the GEMM then reads that
+ * operand from the converted copy (no 1/2 for it).  The conversion is exact except for the 15 magnitudes
+ * below 2^-6, which lie between e4m3fn's subnormals and are rounded to nearest-even there (absolute
+ * error <= 2^-10, i.e. <= 4e-6 of a block whose largest magnitude is 240); fnuz NaN stays NaN.  Operands
+ * without special bytes are computed from the caller's bytes, exactly.  Nothing is synchronised and the
+ * result is always written; rf_device_status() afterwards reports detail 16 once if a converted copy was
+ * used (a note, not an error: status word 1 never stops a kernel).  m*k and n*k must be multiples of 16. */
 int rf_fp8_gemm_colmajor_fnuz(const void *a, const void *b, const float *as, const float *bs, void *c, int m,
                               int n, int k, void *workspace, size_t workspace_bytes, rf_stream_t stream);
 
@@ -134,16 +141,32 @@ int rf_fp8_gemm_colmajor_fnuz(const void *a, const void *b, const float *as, con
  *  - All calls on a device share the one array and it keeps the previous call's slices.  Nothing in
  *    it needs clearing (every slice element is rewritten before it is read), but two calls that can
  *    overlap on the GPU (different streams without an ordering between them) race on it.
- *  - A bounded device-side wait that expires is recorded in a status word private to this path.  */
+ *  - A bounded device-side wait that expires is recorded in a status area private to this path;
+ *    rf_fp8_gemm_static_status reads and clears it.                                                */
 #define RF_STATIC_SCRATCH_BYTES (16u << 20)
 int rf_fp8_gemm_static_scratch(const void *a, const void *b, const float *as, const float *bs, void *c, int m,
                                int n, int k, int split_k, rf_stream_t stream);
 
-/* Reads and clears the device-side status word of the current device
- * (synchronises the device).  Returns RF_OK or RF_ERR_DEVICE_TIMEOUT; the raw
- * device code is stored in *detail when detail != NULL.
- * Reference: none - the reference aborts (include/gpu_libs.h:31-37).          */
+/* rf_device_status for the allocation-free path (no counterpart in the reference): synchronises the
+ * device, reads the path's own status area through the symbol's device address, clears it and returns
+ * RF_OK or RF_ERR_DEVICE_TIMEOUT with the device code in *detail.  Allocates nothing.  While a code is
+ * recorded, kernels of this path give up their waits early, so call it after a failure.             */
+int rf_fp8_gemm_static_status(int *detail);
+
+/* Reads and clears the device-side status area of the current device (synchronises the device).
+ * Word 0 holds the code of the first bounded device-side wait that expired (1-6: producer, MMA waiting
+ * for data, MMA waiting for TMEM, epilogue, scheduler / rendezvous, store); while it is set, kernels give
+ * up their waits early and their output is incomplete, so callers that care check after a step.  Word 1
+ * holds notes that stop nothing (16: an e4m3fnuz operand was computed from converted bytes; 32: an
+ * expert-parallel receive buffer overflowed and rows were dropped).  Returns RF_OK when both are zero,
+ * else RF_ERR_DEVICE_TIMEOUT with word 0 (or, if that is zero, word 1) in *detail.
+ * Reference: none - the reference aborts (include/gpu_libs.h:31-37).                                 */
 int rf_device_status(int *detail);
+
+/* Limit of every bounded device-side wait on the current device, in nanoseconds (0 = the default, 2 s).
+ * Stored in the status area and read by the kernels when a wait runs long; takes effect for kernels
+ * launched afterwards.  No reference counterpart.                                                  */
+int rf_set_wait_limit_ns(unsigned long long limit_ns);
 
 /* ------------------------------------------------------------------- MoE -- */
 
@@ -291,6 +314,15 @@ int rf_moe_grouped_gemm(const void *x, int n_rows, const void *const *w_ptrs_hos
                         const void *const *w2_ptrs_host, const int *group_offsets_dev, int n_groups, int n_dim,
                         int k_dim, void *out, rf_stream_t stream);
 
+/* The grouped GEMM addresses each expert's weight through a TMA descriptor; the device arrays of
+ * descriptors are cached per set of weight pointers (2048 sets by default, least recently used evicted,
+ * freed only after the kernels that may read them have finished).  A set is built at a layer's first
+ * call (one cudaMalloc and one blocking copy), so keep warm-up calls outside stream capture.  The MoE
+ * entry points of one device share that cache and one tile-list scratch: issue them on one stream at a
+ * time, as the reference does (src/moe/moe.cpp:580-583).  max_sets >= 4.  No reference counterpart
+ * (hipBLASLt takes raw pointers, src/moe/gemm_thirdparty.cpp:65-115).                               */
+int rf_moe_set_map_cache_sets(int max_sets);
+
 /* Router logits expert_scores[t, e] = fp16(x[t,:] . router_weight[e,:] + router_bias[e]); the
  * matmul the reference leaves to PyTorch (scripts/gen_submission.py:400).  router_bias may be NULL. */
 int rf_moe_router_gemm(const void *x, const void *router_weight, const float *router_bias, int n_tokens,
@@ -341,9 +373,11 @@ int rf_moe_ep_rendezvous(void *const *sync_all, const int *counts_dev, int n_cou
 /* Expert-parallel layout: from the all-gathered pair counts counts_all_dev [world][n_experts]
  * computes, on the device, where this rank's rows land in the owners' receive buffers
  * (send_base_dev [n_experts]) and the row ranges of this rank's own experts
- * (recv_offsets_dev [n_experts/world + 1]).  Expert e lives on rank e / (n_experts/world).   */
-int rf_moe_ep_layout(const int *counts_all_dev, int rank, int world, int n_experts, int *send_base_dev,
-                     int *recv_offsets_dev, rf_stream_t stream);
+ * (recv_offsets_dev [n_experts/world + 1]).  Expert e lives on rank e / (n_experts/world).
+ * `capacity` = rows of the receive buffers: row ranges are clipped to it and an overflow is noted in
+ * the device status area (detail 32).                                                         */
+int rf_moe_ep_layout(const int *counts_all_dev, int rank, int world, int n_experts, int capacity,
+                     int *send_base_dev, int *recv_offsets_dev, rf_stream_t stream);
 
 /* Dispatch: the token-row gather of expand_input (src/moe/moe_topk_kernel.cpp:174-213) writing
  * directly into the owner ranks' receive buffers `recv_x_all[r]` (fp16 [capacity, d_hidden]).
@@ -351,11 +385,15 @@ int rf_moe_ep_layout(const int *counts_all_dev, int rank, int world, int n_exper
  * sends to rank r+1 first, then r+2, ... so the senders never all target one GPU.
  * recv_meta_all (may be NULL): every rank's int32 [capacity] return-address table; beside row i of
  * recv_x_all[q] the sender writes recv_meta_all[q][i] = (rank << 28) | p, p = position of the pair in
- * the sender's expert-sorted order - the row_dest_dev input of rf_moe_grouped_gemm_scatter.       */
+ * the sender's expert-sorted order - the row_dest_dev input of rf_moe_grouped_gemm_scatter.
+ * A pair whose destination row is >= capacity is NOT sent (nothing is ever written past a peer's
+ * allocation): pair_rank = -1, status detail 32, and with drop_fill != NULL (this rank's fp16
+ * [n_pairs, d_hidden] result rows, push variant) the pair's result row is zeroed instead.          */
 int rf_moe_ep_dispatch(const void *x, const int *permuted_experts, const int *permuted_rows,
                        const int *first_token_offset, const int *send_base, int n_tokens, int n_pairs, int d_hidden,
-                       int n_experts, int rank, int world, void *const *recv_x_all, void *const *recv_meta_all,
-                       int *pair_rank, int *pair_row, rf_stream_t stream);
+                       int n_experts, int rank, int world, int capacity, void *const *recv_x_all,
+                       void *const *recv_meta_all, int *pair_rank, int *pair_row, void *drop_fill,
+                       rf_stream_t stream);
 
 /* The experts' second GEMM fused with the way back (no reference counterpart: the reference is single-GPU;
  * it is the grouped fc2 of src/moe/moe.cpp:244-248 whose epilogue performs the row scatter that
@@ -375,6 +413,48 @@ int rf_moe_grouped_gemm_scatter(const void *x, int n_rows, const void *const *w_
 int rf_moe_ep_combine(void *const *y_all, const void *shared_fc2_output, const int *rev_permuted_rows,
                       const void *expanded_seq_softmax, const int *pair_rank, const int *pair_row, int n_tokens,
                       int top_k, int d_hidden, int world, void *final_output, rf_stream_t stream);
+
+/* The expert-parallel layer as one object (no reference counterpart; the host-side sequencing is the
+ * multi-GPU form of run_topk_impl, src/moe/moe.cpp:129-339).  One object per rank, created with that
+ * rank's device current.  It owns every buffer of a step, a side stream, the events and the rendezvous
+ * epochs; rf_moe_ep_forward enqueues one whole step (router GEMM, top-k, sort, count exchange, dispatch
+ * beside the shared expert, routed experts, results home, combine) without host synchronisation,
+ * allocation or collective-library call.  Set-up: create on every rank -> rf_moe_ep_handles -> exchange
+ * the handle blobs between the processes (any transport) -> rf_moe_ep_connect -> a barrier between the
+ * processes -> forward.  Tear-down: barrier -> rf_moe_ep_disconnect on every rank -> barrier -> destroy. */
+typedef struct RfMoeEp RfMoeEp;
+typedef struct {
+    int n_tokens;              /* tokens of THIS rank                                              */
+    int d_hidden, d_expert, n_routed_experts, n_experts_per_token, n_shared_experts;
+    int rank, world;           /* expert e lives on rank e / (n_routed_experts / world)            */
+    int capacity;              /* rows of the receive buffers; 0 = worst case n_tokens*k*world     */
+    int push_results;          /* 1: fc2's epilogue stores the results home; 0: the combine pulls  */
+} RfMoeEpConfig;
+#define RF_MOE_EP_HANDLE_BYTES 256   /* four 64-byte IPC handles per rank */
+int rf_moe_ep_create(const RfMoeEpConfig *config, RfMoeEp **out);
+/* handles: RF_MOE_EP_HANDLE_BYTES of this rank; all_handles: world blobs in rank order.        */
+int rf_moe_ep_handles(RfMoeEp *ep, unsigned char *handles);
+int rf_moe_ep_connect(RfMoeEp *ep, const unsigned char *all_handles);
+/* Device pointers, kept by reference: router [E, d] fp16 (+ optional fp32 bias [E]); HOST arrays of the
+ * n_routed_experts/world LOCAL experts' gate / up [d, f] and down [f, d]; the shared expert's three.    */
+int rf_moe_ep_set_weights(RfMoeEp *ep, const void *router_weight, const float *router_bias,
+                          const void *const *expert_gate, const void *const *expert_up,
+                          const void *const *expert_down, const void *shared_gate, const void *shared_up,
+                          const void *shared_down);
+/* x: fp16 [n_tokens, d_hidden] local tokens -> out fp16 [n_tokens, d_hidden]; asynchronous on `stream`. */
+int rf_moe_ep_forward(RfMoeEp *ep, const void *x, void *out, rf_stream_t stream);
+enum { RF_MOE_EP_OPT_TRACE = 1,            /* value != 0: record an event after every stage of forward   */
+       RF_MOE_EP_OPT_DISPATCH_BLOCKS = 2   /* value > 0: grid cap of the dispatch kernel                 */ };
+int rf_moe_ep_set_option(RfMoeEp *ep, int option, int value);
+/* Milliseconds of the stages of the last traced forward (synchronises); returns the number of stages.  */
+int rf_moe_ep_stage_times(RfMoeEp *ep, float *ms, const char **names, int max_stages);
+/* Device buffers of the last step, for tests: router logits fp16 [T, E]; top-k indices int32 [T, k]; the
+ * all-gathered counts int32 [world, E]; send_base int32 [E]; recv_offsets int32 [E/world + 1]; pair_rank. */
+enum { RF_MOE_EP_BUF_SCORES = 0, RF_MOE_EP_BUF_INDEX = 1, RF_MOE_EP_BUF_COUNTS_ALL = 2,
+       RF_MOE_EP_BUF_SEND_BASE = 3, RF_MOE_EP_BUF_RECV_OFFSETS = 4, RF_MOE_EP_BUF_PAIR_RANK = 5 };
+int rf_moe_ep_buffer(RfMoeEp *ep, int which, void **ptr, size_t *bytes);
+int rf_moe_ep_disconnect(RfMoeEp *ep);
+int rf_moe_ep_destroy(RfMoeEp *ep);
 
 /* Library / build identification: "rf_b200 <version> sm_100a".               */
 const char *rf_version(void);

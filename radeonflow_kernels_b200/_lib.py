@@ -73,6 +73,7 @@ def lib() -> ctypes.CDLL:
                 "(there is no CPU or PyTorch fallback)")
         _lib = ctypes.CDLL(LIB_PATH)
         _declare(_lib)
+        _declare_ep(_lib)
     return _lib
 
 
@@ -102,6 +103,10 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_fp8_gemm_colmajor_fnuz.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp, sz, vp]
     L.rf_fp8_gemm_static_scratch.restype = ci
     L.rf_fp8_gemm_static_scratch.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
+    L.rf_fp8_gemm_static_status.restype = ci
+    L.rf_fp8_gemm_static_status.argtypes = [ctypes.POINTER(ci)]
+    L.rf_set_wait_limit_ns.restype = ci
+    L.rf_set_wait_limit_ns.argtypes = [ctypes.c_ulonglong]
     # ---- MoE
     pm = ctypes.POINTER(PerfMetrics)
     raw = ctypes.POINTER(MoEInputRaw)
@@ -131,6 +136,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_moe_grouped_gemm.argtypes = [vp, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), vp, ci, ci, ci, vp, vp]
     L.rf_moe_router_gemm.restype = ci
     L.rf_moe_router_gemm.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp]
+    L.rf_moe_set_map_cache_sets.restype = ci
+    L.rf_moe_set_map_cache_sets.argtypes = [ci]
     L.rf_moe_combine.restype = ci
     L.rf_moe_combine.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, vp]
     # ---- multi-GPU
@@ -151,13 +158,51 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_moe_ep_rendezvous.restype = ci
     L.rf_moe_ep_rendezvous.argtypes = [pvp, vp, ci, ci, ci, ci, vp]
     L.rf_moe_ep_layout.restype = ci
-    L.rf_moe_ep_layout.argtypes = [vp, ci, ci, ci, vp, vp, vp]
+    L.rf_moe_ep_layout.argtypes = [vp, ci, ci, ci, ci, vp, vp, vp]
     L.rf_moe_ep_dispatch.restype = ci
-    L.rf_moe_ep_dispatch.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, pvp, pvp, vp, vp, vp]
+    L.rf_moe_ep_dispatch.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, pvp, pvp, vp, vp, vp, vp]
     L.rf_moe_grouped_gemm_scatter.restype = ci
     L.rf_moe_grouped_gemm_scatter.argtypes = [vp, ci, pvp, vp, ci, ci, ci, vp, pvp, ci, vp]
     L.rf_moe_ep_combine.restype = ci
     L.rf_moe_ep_combine.argtypes = [pvp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, vp]
+
+
+class RfMoeEpConfig(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "n_tokens", "d_hidden", "d_expert", "n_routed_experts", "n_experts_per_token", "n_shared_experts",
+        "rank", "world", "capacity", "push_results")]
+
+
+RF_MOE_EP_HANDLE_BYTES = 256
+(RF_MOE_EP_BUF_SCORES, RF_MOE_EP_BUF_INDEX, RF_MOE_EP_BUF_COUNTS_ALL, RF_MOE_EP_BUF_SEND_BASE,
+ RF_MOE_EP_BUF_RECV_OFFSETS, RF_MOE_EP_BUF_PAIR_RANK) = range(6)
+RF_MOE_EP_OPT_TRACE, RF_MOE_EP_OPT_DISPATCH_BLOCKS = 1, 2
+
+
+def _declare_ep(L: ctypes.CDLL) -> None:
+    vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    pvp = ctypes.POINTER(vp)
+    pub = ctypes.POINTER(ctypes.c_ubyte)
+    L.rf_moe_ep_create.restype = ci
+    L.rf_moe_ep_create.argtypes = [ctypes.POINTER(RfMoeEpConfig), pvp]
+    L.rf_moe_ep_handles.restype = ci
+    L.rf_moe_ep_handles.argtypes = [vp, pub]
+    L.rf_moe_ep_connect.restype = ci
+    L.rf_moe_ep_connect.argtypes = [vp, pub]
+    L.rf_moe_ep_set_weights.restype = ci
+    L.rf_moe_ep_set_weights.argtypes = [vp, vp, vp, pvp, pvp, pvp, vp, vp, vp]
+    L.rf_moe_ep_forward.restype = ci
+    L.rf_moe_ep_forward.argtypes = [vp, vp, vp, vp]
+    L.rf_moe_ep_set_option.restype = ci
+    L.rf_moe_ep_set_option.argtypes = [vp, ci, ci]
+    L.rf_moe_ep_stage_times.restype = ci
+    L.rf_moe_ep_stage_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_char_p), ci]
+    L.rf_moe_ep_buffer.restype = ci
+    L.rf_moe_ep_buffer.argtypes = [vp, ci, pvp, ctypes.POINTER(sz)]
+    L.rf_moe_ep_disconnect.restype = ci
+    L.rf_moe_ep_disconnect.argtypes = [vp]
+    L.rf_moe_ep_destroy.restype = ci
+    L.rf_moe_ep_destroy.argtypes = [vp]
 
 
 def check(status: int, what: str) -> None:

@@ -42,6 +42,13 @@ __device__ unsigned long long g_wait_stats[8];
 #define RF_STAT_FLUSH(idx, acc)
 #endif
 
+// RF_EPI_WIDE=1 selects an experimental epilogue inner loop (64 staging registers reloaded in place, the
+// accumulator buffer handed back after two load latencies).  Measured on B200 it is not faster: built without
+// spills it needs the K loop un-unrolled and runs 6144 x 4608 x 7168 in 191 us against 178 us for the default.
+#ifndef RF_EPI_WIDE
+#define RF_EPI_WIDE 0
+#endif
+
 namespace {
 
 constexpr int BM = 128;
@@ -84,8 +91,19 @@ struct GemmCfg {
     static constexpr int kSmemBytes =
         STAGES * kStageBytes + kEpiWarps * kSlabs * kSlabBytes + kBarBytes + 1024;       // + alignment slack
     // The epilogue (64 or 128 accumulators per thread plus staging) wants more than the 168 registers a
-    // 384-thread CTA starts with, the producer warpgroup far fewer: registers are rebalanced.
+    // 384-thread CTA starts with, the producer warpgroup far fewer: registers are rebalanced after set-up
+    // (128 * kRegsLo + 256 * kRegsHi <= 64512, the CTA's allocation at 168 per thread).  Measured on the
+    // 18-shape sweep: 120 / 192 is the fastest split for the default epilogue.
     static constexpr bool kRebalanceRegs = true;
+#if defined(RF_REGS_LO) && defined(RF_REGS_HI)
+    static constexpr int kRegsLo = RF_REGS_LO, kRegsHi = RF_REGS_HI;
+#elif RF_EPI_WIDE
+    static constexpr int kRegsLo = kColsPerThread > 64 ? 40 : 104;
+    static constexpr int kRegsHi = kColsPerThread > 64 ? 232 : 200;
+#else
+    static constexpr int kRegsLo = 120, kRegsHi = 192;
+#endif
+    static_assert(128 * kRegsLo + 256 * kRegsHi <= 64512 && kRegsLo % 8 == 0 && kRegsHi % 8 == 0, "register split");
     static_assert(kColsPerThread == 64 || kColsPerThread == 128, "epilogue handles 64 or 128 columns per thread");
     static_assert(kTmemCols == 512, "TMEM columns: power of two, at most 512");
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -146,7 +164,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #ifdef RF_SINGLE_ISSUE
     constexpr bool kDualIssue = false;
 #else
-    constexpr bool kDualIssue = !TWO && (NBUF % 2 == 0);
+    constexpr bool kDualIssue = NBUF % 2 == 0;
 #endif
     const uint32_t cta_rank = TWO ? cluster_ctarank() : 0u;      // 0 = leader of the pair
     const int unit = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;          // work-loop index
@@ -190,16 +208,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const int kb_total = p.k / BK;
 
     if (warp < NUM_NON_EPI_WARPS) {
-// Register split after set-up: 4 producer / MMA warps at RF_REGS_LO, 8 epilogue warps at RF_REGS_HI
-// (128 * LO + 256 * HI <= 64512, the CTA's allocation at 168 per thread).  Measured on the 18-shape sweep:
-// 120 / 192 is the fastest split; 104 / 200 is 5 % slower, 208 and above 1.5x slower.
-#ifndef RF_REGS_LO
-#define RF_REGS_LO 120
-#define RF_REGS_HI 192
-#endif
-#define RF_STR2(x) #x
-#define RF_STR(x) RF_STR2(x)
-    if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 " RF_STR(RF_REGS_LO) ";\n");
+    // Register split after set-up: the 4 producer / MMA warps shrink to kRegsLo, the 8 epilogue warps grow
+    // to kRegsHi.
+    if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(Cfg::kRegsLo));
     // Producer and MMA warps keep all 32 lanes in the loops (warp-uniform control
     // flow, so descriptors and addresses live in uniform registers) and elect one
     // lane only for the instructions that must be issued once.
@@ -208,6 +219,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         uint32_t it = 0;  // running K-block counter across work items
         bool ok = true;
         long long w_empty = 0; (void)w_empty;
+        // e4m3fnuz operands (reference-layout configurations only): an operand that holds +-240 or NaN bytes
+        // is read from its converted copy (the conversion pass that ran before this kernel left the flags)
+        const CUtensorMap* map_a = &tma_a;
+        const CUtensorMap* map_b = &tma_b;
+        if (Cfg::kMnMajor && p.fnuz_flags != nullptr) {
+            if (p.fnuz_flags[0] != 0) map_a = &dests.m[0];
+            if (p.fnuz_flags[1] != 0) map_b = &dests.m[1];
+        }
         for (int w = unit; w < total_work && ok; w += unit_stride) {
             const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
             const int kb0 = (int)((long long)kb_total * t.split / p.splits);
@@ -219,7 +238,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 { RF_STAT_BEGIN();
-                ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1, p.status, kErrProducerWait));
+                ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1, p.status, kErrProducerWait, p.launch_tag));
                 RF_STAT_END(w_empty); }
                 if (!ok) break;
                 if (elect_one()) {
@@ -227,10 +246,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                     const uint32_t sa = smem_base + s * Cfg::kStageBytes;
                     if (Cfg::kMnMajor) {
                         // boxes of 128 K-rows x 128 bytes of M (or N); B needs one box per 128 columns
-                        tma_load_2d(sa, &tma_a, full_bar(s), a_row0, kb * BK);
+                        tma_load_2d(sa, map_a, full_bar(s), a_row0, kb * BK);
 #pragma unroll
                         for (int j = 0; j < BN / 128; ++j)
-                            tma_load_2d(sa + Cfg::kABytes + j * (BK * 128), &tma_b, full_bar(s), b_row0 + 128 * j,
+                            tma_load_2d(sa + Cfg::kABytes + j * (BK * 128), map_b, full_bar(s), b_row0 + 128 * j,
                                         kb * BK);
                     } else {
                         tma_load_2d(sa, &tma_a, full_bar(s), kb * BK, a_row0);
@@ -256,7 +275,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         constexpr uint32_t kstep = Cfg::kMnMajor ? (UMMA_K * 128) / 16 : UMMA_K / 16;
         uint32_t it = 0;
         bool ok = true;
-        long long w_tmem = 0, w_full = 0; (void)w_tmem; (void)w_full;
+        long long w_tmem = 0, w_full = 0, w_issue = 0; (void)w_tmem; (void)w_full; (void)w_issue;
         for (int w = unit; w < total_work && ok; w += unit_stride) {
             const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
             const int kb0 = (int)((long long)kb_total * t.split / p.splits);
@@ -270,7 +289,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 if (TWO && cta_rank != 0) {
                     // Second CTA of the pair: it issues no MMA.  This warp relays "my stage has landed"
                     // to the leader (a TMA load can only signal a barrier of the CTA it writes to).
-                    ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, kErrMmaWaitFull));
+                    ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, kErrMmaWaitFull, p.launch_tag));
                     if (!ok) break;
                     // (no memory ordering needed: the stage was written by the TMA and is read by the
                     // tensor core, both through the async proxy; the barrier flip means the bytes landed)
@@ -279,20 +298,21 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                     continue;
                 }
                 { RF_STAT_BEGIN();
-                ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(buf), bph ^ 1, p.status, kErrMmaWaitTmem));
+                ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(buf), bph ^ 1, p.status, kErrMmaWaitTmem, p.launch_tag));
                 RF_STAT_END(w_tmem); }
                 if (!ok) break;
                 { RF_STAT_BEGIN();
-                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, kErrMmaWaitFull));
+                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, kErrMmaWaitFull, p.launch_tag));
                 RF_STAT_END(w_full); }
                 if (!ok) break;
                 if (TWO) {
                     RF_STAT_BEGIN();
-                    ok = __all_sync(0xffffffffu, mbar_wait(peer_full_bar(s), ph, p.status, kErrMmaWaitFull));
+                    ok = __all_sync(0xffffffffu, mbar_wait(peer_full_bar(s), ph, p.status, kErrMmaWaitFull, p.launch_tag));
                     RF_STAT_END(w_full);
                     if (!ok) break;
                 }
                 tc_fence_after();
+                RF_STAT_BEGIN();
                 const uint32_t sa = smem_base + s * Cfg::kStageBytes;
                 const uint64_t adesc = Cfg::kMnMajor ? smem_desc_mnmajor_sw128(sa, BK * 128, 1024)
                                                      : smem_desc_kmajor_sw128(sa);
@@ -312,13 +332,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                     else umma_commit(tmem_full_bar(buf));
                 }
                 __syncwarp();
+                RF_STAT_END(w_issue);
             }
         }
-        if (lane == 0) { RF_STAT_FLUSH(1, w_tmem); RF_STAT_FLUSH(2, w_full); }
+        if (lane == 0) { RF_STAT_FLUSH(1, w_tmem); RF_STAT_FLUSH(2, w_full); RF_STAT_FLUSH(6, w_issue); }
     }
     } else {
         // ---------------------------------------------------------- epilogue
-        if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 " RF_STR(RF_REGS_HI) ";\n");
+        if (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(Cfg::kRegsHi));
         const int ew = warp - NUM_NON_EPI_WARPS;
         const int quad = warp & 3;            // TMEM lane quadrant this warp may access
         const int grp = ew >> 2;              // column group
@@ -327,36 +348,55 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         uint32_t it = 0;
         uint32_t n_stores = 0;        // tile-store chunks issued by this warp so far
         bool ok = true;
-        long long w_acc = 0, w_total = 0; (void)w_acc; (void)w_total;
+        long long w_acc = 0, w_total = 0, w_rel = 0; (void)w_acc; (void)w_total; (void)w_rel;
 #ifdef RF_WAIT_STATS
         const long long t_begin = clock64();
 #endif
         // (in a CTA pair tmem_empty lives in the leader CTA, the only MMA issuer; both CTAs arrive on it
         // through the cluster window)
         for (int w = unit; w < total_work && ok; w += unit_stride) {
-            const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
-            const int kb0 = (int)((long long)kb_total * t.split / p.splits);
-            const int kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
-            const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
-            const int row = cta_m_blk * BM + row_in_tile;
-            const int col0 = t.n_blk * BN + grp * CPT;
-            const bool row_ok = row < p.m;
-            const int nb = col0 >> 7;
-            const bool nb_ok = col0 < p.n;
-            const float* as_row = p.a_scale + (size_t)(row_ok ? row : 0) * p.as_row_stride;
-            const float* bs_row = p.b_scale + (size_t)(nb_ok ? nb : 0) * p.bs_row_stride;
+            // (the tile's coordinates are decoded again after the K loop for the store: nothing but the
+            // accumulators, the staging buffers and the scale queue should stay live across that loop)
+            int kb0, kb1;
+            long long as_off, bs_off;      // element offsets of this thread's scale rows
+            {
+                const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
+                kb0 = (int)((long long)kb_total * t.split / p.splits);
+                kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
+                const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
+                const int row = cta_m_blk * BM + row_in_tile;
+                const int col0 = t.n_blk * BN + grp * CPT;
+                as_off = (long long)(row < p.m ? row : 0) * p.as_row_stride;
+                bs_off = (long long)(col0 < p.n ? (col0 >> 7) : 0) * p.bs_row_stride;
+            }
+            const float* as_row = p.a_scale + as_off;
+            const float* bs_row = p.b_scale + bs_off;
             // K-major scale tables have unit stride along K (a compile-time fact the address arithmetic
             // of the prefetch queue depends on); only the reference's [k/128][m] tables stride by m
             const int as_ks = Cfg::kMnMajor ? (int)p.as_k_stride : 1;
             const int bs_ks = Cfg::kMnMajor ? (int)p.bs_k_stride : 1;
+            // out_scale (reference-layout configurations only): 1 for e4m3fn bytes.  e4m3fnuz bytes read as
+            // e4m3fn are twice their value, so each operand that is consumed unconverted contributes 1/2; an
+            // operand read from its converted copy (true values) contributes 1.  A power of two commutes
+            // exactly with every rounding of the fp32 accumulation.
+            float out_scale = 1.0f;
+            if (Cfg::kMnMajor && p.fnuz_flags != nullptr)
+                out_scale = (p.fnuz_flags[0] != 0 ? 1.0f : 0.5f) * (p.fnuz_flags[1] != 0 ? 1.0f : 0.5f);
 
             float2 acc[CPT / 2];
 #pragma unroll
             for (int j = 0; j < CPT / 2; ++j) acc[j] = make_float2(0.f, 0.f);
-
+#if RF_EPI_WIDE
+            // two 32-column staging buffers, reloaded in place
+            float v[2][32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[0][j] = v[1][j] = 0.f;
+            constexpr int PF = 3;
+#else
+            constexpr int PF = 4;
+#endif
             // Scale loads run PF K blocks ahead of their use so their latency
             // (L2 or HBM) never sits on the per-K-block critical path.
-            constexpr int PF = 4;
             float qa[PF], qb[PF];
 #pragma unroll
             for (int d = 0; d < PF; ++d) {
@@ -364,12 +404,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 qa[d] = __ldg(as_row + kk * as_ks);
                 qb[d] = __ldg(bs_row + kk * bs_ks);
             }
+#if RF_EPI_WIDE
+#pragma unroll 1
+#else
 #pragma unroll 4
+#endif
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                // out_scale (reference-layout configurations only): 1, or 1/4 when the bytes are e4m3fnuz,
-                // which read as e4m3fn are twice their value in each operand.  A power of two commutes
-                // exactly with every rounding of the fp32 accumulation.
-                const float s = Cfg::kMnMajor ? qa[0] * qb[0] * p.out_scale : qa[0] * qb[0];
+                const float s = Cfg::kMnMajor ? qa[0] * qb[0] * out_scale : qa[0] * qb[0];
 #pragma unroll
                 for (int d = 0; d + 1 < PF; ++d) { qa[d] = qa[d + 1]; qb[d] = qb[d + 1]; }
                 {
@@ -381,7 +422,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 const int buf = it % NBUF;
                 const uint32_t bph = (it / NBUF) & 1;
                 { RF_STAT_BEGIN();
-                if (!mbar_wait(tmem_full_bar(buf), bph, p.status, kErrEpilogueWait)) { ok = false; break; }
+                if (!mbar_wait(tmem_full_bar(buf), bph, p.status, kErrEpilogueWait, p.launch_tag)) { ok = false; break; }
                 RF_STAT_END(w_acc); }
                 tc_fence_after();
                 // The MMAs that wrote this buffer have finished reading their smem stage.
@@ -396,6 +437,37 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                         else mbar_arrive(tmem_empty_bar(buf));
                     }
                 };
+                RF_STAT_BEGIN();
+#if RF_EPI_WIDE
+                // The first 64 columns are requested together (two loads: one 64-column load would need 64
+                // consecutive registers, which costs spills); while their FMAs run, the loads of the next two
+                // 32-column chunks are already in flight, so the accumulator buffer is handed back after two
+                // load latencies (one, when the thread owns only 64 columns); the last FMAs run after that.
+                auto fma_chunk = [&](int c, const float (&x)[32]) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        acc[c * 16 + j] = __ffma2_rn(make_float2(x[2 * j], x[2 * j + 1]), s2, acc[c * 16 + j]);
+                };
+                tmem_ld32_async_inplace(taddr, v[0]);
+                tmem_ld32_async_inplace(taddr + 32, v[1]);
+                tmem_ld_fence2(v[0], v[1]);
+                if (NCH == 2) {
+                    release_buffer();
+                    RF_STAT_END(w_rel);
+                    fma_chunk(0, v[0]);
+                    fma_chunk(1, v[1]);
+                } else {
+                    fma_chunk(0, v[0]);
+                    tmem_ld32_async_inplace(taddr + 64, v[0]);
+                    fma_chunk(1, v[1]);
+                    tmem_ld32_async_inplace(taddr + 96, v[1]);
+                    tmem_ld_fence2(v[0], v[1]);
+                    release_buffer();
+                    RF_STAT_END(w_rel);
+                    fma_chunk(2, v[0]);
+                    fma_chunk(3, v[1]);
+                }
+#else
                 // Staging registers: two 32-column buffers (the load of chunk c+1 overlaps the FMAs of
                 // chunk c) when a thread owns 64 columns; one buffer when it owns 128, because 128
                 // accumulators leave no room for a second one (the other epilogue warp on the same
@@ -407,25 +479,82 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 for (int c = 0; c < NCH; ++c) {
                     tmem_ld_fence(v[c % NV]);   // waits for every load issued so far
                     if (NV == 2 && c + 1 < NCH) tmem_ld32_async(taddr + (c + 1) * 32, v[(c + 1) % NV]);
-                    if (c + 1 == NCH) release_buffer();
+                    if (c + 1 == NCH) { release_buffer(); RF_STAT_END(w_rel); }
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         acc[c * 16 + j] =
                             __ffma2_rn(make_float2(v[c % NV][2 * j], v[c % NV][2 * j + 1]), s2, acc[c * 16 + j]);
                     if (NV == 1 && c + 1 < NCH) tmem_ld32_async(taddr + (c + 1) * 32, v[0]);
                 }
+#endif
             }
             if (!ok) break;
-            // Tile store: each warp stages its 32 rows x 128 bytes in its own swizzled
-            // shared-memory slab and one lane hands the slab to the TMA, which writes
-            // full 128-byte row segments and clips rows >= m / columns >= n.
+            // Tile store.  Each warp transposes its 32 rows x 128 bytes through its own swizzled shared-memory
+            // slab so that global memory is written in whole 128-byte row segments.
             {
-                // consecutive stores of this warp alternate over its kSlabs slabs (n_stores counts them across
-                // tiles, so skipped chunks of a ragged tile cannot break the alternation); before a slab is
-                // rewritten, the store that last read it (kSlabs commit groups ago) must have finished reading
                 constexpr int SL = Cfg::kSlabs;
+                const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
+                const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
+                const int col0 = t.n_blk * BN + grp * CPT;
                 const uint32_t slab0 = slab_base + ew * SL * Cfg::kSlabBytes;
                 const int slab_row0 = cta_m_blk * BM + quad * 32;
+                if (p.direct_store && p.n_dest <= 1) {
+                    // Default for one destination: the warp reads the slab back row-segment-wise (8 lanes per
+                    // 128-byte segment) and stores it with ordinary vector stores.  Unlike a TMA store the slab
+                    // is free again as soon as those loads have returned, so the 2 (fp32 slices: 4) chunks of a
+                    // tile follow each other without waiting for an asynchronous read of the slab; the MMA warps
+                    // sit idle behind this phase once both accumulator buffers of the next tile are full.
+                    const uint32_t my_row = slab0 + lane * 128;
+                    const int c8 = lane & 7, rsub = lane >> 3;
+                    if (p.splits == 1) {
+#pragma unroll
+                        for (int ch = 0; ch < CPT / 64; ++ch) {
+                            if (col0 + ch * 64 >= p.n) break;
+                            __syncwarp();            // every lane has read the previous chunk out of the slab
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int a0 = ch * 32 + j * 4;
+                                st_shared_v4(my_row + ((j ^ (lane & 7)) << 4),
+                                             pack_bf16x2(acc[a0 + 0].x, acc[a0 + 0].y), pack_bf16x2(acc[a0 + 1].x, acc[a0 + 1].y),
+                                             pack_bf16x2(acc[a0 + 2].x, acc[a0 + 2].y), pack_bf16x2(acc[a0 + 3].x, acc[a0 + 3].y));
+                            }
+                            __syncwarp();
+                            __nv_bfloat16* dst = p.c + (size_t)slab_row0 * p.n + (col0 + ch * 64 + 8 * c8);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int r = 4 * i + rsub;
+                                const uint4 q = ld_shared_v4(slab0 + r * 128 + ((c8 ^ (r & 7)) << 4));
+                                if (slab_row0 + r < p.m) *reinterpret_cast<uint4*>(dst + (size_t)r * p.n) = q;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int ch = 0; ch < CPT / 32; ++ch) {
+                            if (col0 + ch * 32 >= p.n) break;
+                            __syncwarp();
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int a0 = ch * 16 + j * 2;
+                                st_shared_v4(my_row + ((j ^ (lane & 7)) << 4), __float_as_uint(acc[a0].x),
+                                             __float_as_uint(acc[a0].y), __float_as_uint(acc[a0 + 1].x),
+                                             __float_as_uint(acc[a0 + 1].y));
+                            }
+                            __syncwarp();
+                            float* dst = p.partial + ((size_t)t.split * p.m + slab_row0) * p.n + (col0 + ch * 32 + 4 * c8);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int r = 4 * i + rsub;
+                                const uint4 q = ld_shared_v4(slab0 + r * 128 + ((c8 ^ (r & 7)) << 4));
+                                if (slab_row0 + r < p.m) *reinterpret_cast<uint4*>(dst + (size_t)r * p.n) = q;
+                            }
+                        }
+                    }
+                } else
+                // TMA form (several destinations, or direct_store off): one lane hands the slab to the TMA, which
+                // clips rows >= m / columns >= n.  Consecutive stores of this warp alternate over its kSlabs slabs
+                // (n_stores counts them across tiles, so skipped chunks of a ragged tile cannot break the
+                // alternation); before a slab is rewritten, the store that last read it (kSlabs commit groups
+                // ago) must have finished reading.
                 if (p.splits == 1) {
 #pragma unroll
                     for (int ch = 0; ch < CPT / 64; ++ch) {
@@ -498,6 +627,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         if (warp == NUM_NON_EPI_WARPS && lane == 0) {
             RF_STAT_FLUSH(3, w_acc);
             RF_STAT_FLUSH(4, clock64() - t_begin);
+            RF_STAT_FLUSH(5, w_rel);
         }
 #endif
     }
@@ -532,14 +662,34 @@ splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restric
     *reinterpret_cast<uint2*>(c + i) = q;
 }
 
-// Flags e4m3fnuz bytes that have no e4m3fn counterpart when read as twice their value: 0x80 (NaN in
-// fnuz, -0 in fn) and 0x7F / 0xFF (+-240 in fnuz, NaN in fn).  Sets *status to kErrFnuzByte.
+// e4m3fnuz -> e4m3fn at equal value, one pass over an operand.
+//
+// The GEMM reads e4m3fnuz bytes as e4m3fn (twice the value, exactly, folded into the scale product) - except
+// that 0x7F / 0xFF (+-240, the largest fnuz magnitudes, present in every block of amax-scaled data) read as
+// NaN and 0x80 (the fnuz NaN) reads as -0.  This pass writes, for the whole operand, the e4m3fn byte of the
+// SAME value: byte - 8 for exponent fields >= 2; the 15 magnitudes below 2^-6 fall between e4m3fn's
+// subnormals and are rounded to nearest-even on that grid (absolute error <= 2^-10); 0x80 becomes the e4m3fn
+// NaN.  If the operand holds one of the three special bytes its flag is raised and the GEMM launched next
+// on the stream reads the converted copy; otherwise the GEMM uses the original bytes and stays exact.
 __global__ void __launch_bounds__(256)
-fnuz_check_kernel(const uint4* __restrict__ bytes, size_t n_vec, int* status) {
-    bool bad = false;
+fnuz_convert_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n_vec, int* __restrict__ flag,
+                    int* __restrict__ status) {
+    __shared__ uint8_t lut[256];
+    {
+        const uint32_t b = threadIdx.x;
+        const uint32_t sign = b & 0x80u, x = b & 0x7Fu;
+        uint32_t o;
+        if (b == 0x80u) o = 0x7Fu;                                    // NaN stays NaN
+        else if (x >= 16u) o = sign | (x - 8u);                       // same value, exponent field one lower
+        else o = sign | ((x + ((x >> 1) & 1u)) >> 1);                 // x * 2^-10 on the 2^-9 grid, nearest-even
+        lut[b] = (uint8_t)o;
+    }
+    __syncthreads();
+    bool special = false;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
-        const uint4 q = __ldg(bytes + i);
+        const uint4 q = __ldg(src + i);
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t x = w[j];
@@ -549,16 +699,23 @@ fnuz_check_kernel(const uint4* __restrict__ bytes, size_t n_vec, int* status) {
             // a byte equals 0x80  <=>  low 7 bits zero and bit 7 set
             const uint32_t low_zero = ~((m7f + 0x7F7F7F7Fu) | 0x7F7F7F7Fu);   // bit 7 set where low 7 bits == 0
             const uint32_t is80 = low_zero & x & 0x80808080u;
-            bad |= (is7f | is80) != 0;
+            special |= (is7f | is80) != 0;
+            o[j] = (uint32_t)lut[x & 0xFFu] | ((uint32_t)lut[(x >> 8) & 0xFFu] << 8) |
+                   ((uint32_t)lut[(x >> 16) & 0xFFu] << 16) | ((uint32_t)lut[x >> 24] << 24);
         }
+        dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    if (bad) atomicCAS(status, 0, (int)kErrFnuzByte);
+    if (special) {
+        *flag = 1;
+        atomicOr(status + kStatusDiagWord, (int)kDiagFnuzByte);
+    }
 }
 
 using Cfg128 = GemmCfg<128, 6>;
 using Cfg256 = GemmCfg<256, 4>;
 using Cfg256ShortK = GemmCfg<256, 3, false, false, 2>;     // K <= 512: tiles of at most four K blocks
 using CfgPair = GemmCfg<256, 6, true>;      // 256 x 256 tile per CTA pair
+using CfgPair128 = GemmCfg<128, 8, true>;   // 256 x 128 tile per CTA pair: four accumulator buffers in TMEM
 using Cfg128Mn = GemmCfg<128, 6, false, true>;
 using Cfg256Mn = GemmCfg<256, 4, false, true>;
 
@@ -640,34 +797,37 @@ extern "C" void rf_debug_wait_stats(unsigned long long* out8, int reset) {
 }
 #endif
 
-cudaError_t fp8_fnuz_check_launch(const void* bytes, size_t n_bytes, int* status, int num_sms,
-                                  cudaStream_t stream) {
+cudaError_t fp8_fnuz_convert_launch(const void* src, void* dst, size_t n_bytes, int* flag, int* status, int num_sms,
+                                    cudaStream_t stream) {
     const size_t n_vec = n_bytes / 16;
-    if (n_vec == 0) return cudaSuccess;
+    cudaError_t e = cudaMemsetAsync(flag, 0, sizeof(int), stream);
+    if (e != cudaSuccess || n_vec == 0) return e;
     size_t blocks = (n_vec + 255) / 256;
     if (blocks > (size_t)num_sms * 8) blocks = (size_t)num_sms * 8;
-    fnuz_check_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(bytes), n_vec, status);
+    fnuz_convert_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst),
+                                                             n_vec, flag, status);
     return cudaGetLastError();
 }
 
+namespace {
+template <class Cfg>
+cudaError_t prepare_cfg() {
+    return cudaFuncSetAttribute(fp8_gemm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+}
+}  // namespace
+
 cudaError_t fp8_gemm_prepare_device() {
-    cudaError_t e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg128::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg256::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256ShortK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg256ShortK::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(fp8_gemm_kernel<CfgPair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             CfgPair::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(fp8_gemm_kernel<Cfg128Mn>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg128Mn::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(fp8_gemm_kernel<Cfg256Mn>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                Cfg256Mn::kSmemBytes);
+    cudaError_t e;
+    if ((e = prepare_cfg<Cfg128>()) != cudaSuccess) return e;
+    if ((e = prepare_cfg<Cfg256>()) != cudaSuccess) return e;
+    if ((e = prepare_cfg<Cfg256ShortK>()) != cudaSuccess) return e;
+    if ((e = prepare_cfg<CfgPair>()) != cudaSuccess) return e;
+    if ((e = prepare_cfg<CfgPair128>()) != cudaSuccess) return e;
+    if ((e = prepare_cfg<Cfg128Mn>()) != cudaSuccess) return e;
+    if ((e = prepare_cfg<Cfg256Mn>()) != cudaSuccess) return e;
+    // the split-K fix-up takes no attribute; querying it loads the function now, not at its first launch
+    cudaFuncAttributes fa;
+    return cudaFuncGetAttributes(&fa, splitk_reduce_kernel);
 }
 
 cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
@@ -678,11 +838,13 @@ cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, 
         for (int i = 0; i < 8; ++i) local.m[i] = tma_c;
         dests = &local;
     }
-    // block_n: 128 / 256 = one-CTA tiles of that width; 512 = the CTA-pair configuration (256 x 256 per pair)
+    // block_n: 128 / 256 = one-CTA tiles of that width; 512 / 384 = the CTA-pair configurations (256 x 256 and
+    // 256 x 128 per pair)
     cudaError_t e = mn_major
                         ? (block_n == 256 ? launch_cfg<Cfg256Mn>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
                                           : launch_cfg<Cfg128Mn>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream))
                     : block_n == 512 ? launch_cfg<CfgPair>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
+                    : block_n == 384 ? launch_cfg<CfgPair128>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
                     : block_n == 256
                         ? (short_k_config(p) ? launch_cfg<Cfg256ShortK>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
                                              : launch_cfg<Cfg256>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream))

@@ -12,7 +12,8 @@ struct GemmParams {
     const float* b_scale;   // [ceil(n/128), k/128]
     __nv_bfloat16* c;       // [m, n]
     float* partial;         // [splits, m, n] fp32 when splits > 1
-    int* status;            // device status word (0 = ok)
+    int* status;            // device status area (status_words.h)
+    int launch_tag;         // tag recorded with an expired wait (host_util: next_launch_tag)
     int m, n, k;
     int tiles_m, tiles_n, splits;
     // Scale addressing: a_scale[row * as_row_stride + kb * as_k_stride] (row-major [m, k/128]: (k/128, 1);
@@ -20,8 +21,10 @@ struct GemmParams {
     long long as_row_stride, as_k_stride, bs_row_stride, bs_k_stride;
     int n_dest;             // copies of C to write (1, or the number of GPUs of an N-split GEMM)
     int c_col_offset;       // column of this GEMM's C inside each destination matrix
-    float out_scale;        // power-of-two factor applied once to the accumulated tile (1, or 1/4 for fnuz bytes)
+    const int* fnuz_flags;  // nullptr, or two device words left by the e4m3fnuz conversion pass (reference-layout
+                            // entry only): [0] / [1] != 0 = read A / B from the converted copy (dests.m[0] / m[1])
     int dest_first;         // first destination to store to (N-split: own rank, so ranks target different GPUs)
+    int direct_store;       // 1: one-destination tiles leave through vector stores (default); 0: through TMA stores
 };
 
 // Output tensor maps of an N-split GEMM: entry d addresses GPU d's full row-major C.
@@ -29,11 +32,13 @@ struct GemmDestMaps {
     CUtensorMap m[8];
 };
 
-// Tile configurations, named by `block_n`: 128 and 256 are one-CTA tiles 128 x block_n; 512 is the
-// CTA-pair configuration (256 x 256 per 2-CTA cluster, each CTA loading 128 rows of A and of B).
-inline int gemm_tile_rows(int block_n) { return block_n == 512 ? 256 : 128; }
-inline int gemm_tile_cols(int block_n) { return block_n == 512 ? 256 : block_n; }
-inline int gemm_b_box_rows(int block_n) { return block_n == 512 ? 128 : block_n; }
+// Tile configurations, named by `block_n`: 128 and 256 are one-CTA tiles 128 x block_n; 512 and 384 are the
+// CTA-pair configurations (256 x 256 and 256 x 128 per 2-CTA cluster, each CTA loading 128 rows of A and
+// half of the tile's rows of B).
+inline bool gemm_is_pair(int block_n) { return block_n == 512 || block_n == 384; }
+inline int gemm_tile_rows(int block_n) { return gemm_is_pair(block_n) ? 256 : 128; }
+inline int gemm_tile_cols(int block_n) { return block_n == 512 ? 256 : (block_n == 384 ? 128 : block_n); }
+inline int gemm_b_box_rows(int block_n) { return block_n == 512 ? 128 : (block_n == 384 ? 64 : block_n); }
 
 // Launches the GEMM (and the split-K fix-up when p.splits > 1) on `stream`.
 // `block_n` is the configuration the tensor map of B and p.tiles_m / p.tiles_n were built for.
@@ -46,9 +51,11 @@ cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, 
                             const CUtensorMap& tma_p, const GemmDestMaps* dests, const GemmParams& p, int block_n,
                             int num_sms, cudaStream_t stream, bool mn_major = false);
 
-// Scans `n_bytes` (multiple of 16) of e4m3fnuz data for bytes that cannot be reinterpreted (0x80, 0x7F,
-// 0xFF); records kErrFnuzByte in *status if one is found.
-cudaError_t fp8_fnuz_check_launch(const void* bytes, size_t n_bytes, int* status, int num_sms, cudaStream_t stream);
+// One pass over `n_bytes` (multiple of 16) of e4m3fnuz data: writes the e4m3fn bytes of equal value to `dst`
+// and sets *flag (device word, cleared first) when the operand holds a byte that cannot be consumed as it
+// is (0x80, 0x7F, 0xFF); in that case kDiagFnuzByte is also OR-ed into the diagnostics word of `status`.
+cudaError_t fp8_fnuz_convert_launch(const void* src, void* dst, size_t n_bytes, int* flag, int* status, int num_sms,
+                                    cudaStream_t stream);
 
 // Sets the launch attributes of every GEMM kernel configuration on the current device (normally done
 // lazily by the first launch of each configuration).

@@ -14,6 +14,7 @@
 #include "fp8_gemm.h"
 #include "host_util.h"
 
+#include <atomic>
 #include <cstdio>
 #include <mutex>
 
@@ -22,11 +23,12 @@ namespace {
 // 16 MiB per GPU that loads the library, held until the process exits.
 constexpr size_t kStaticScratchBytes = RF_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
-// Device status word of this path (bounded waits record their expiry here); zero when the module loads.
-static __device__ int g_static_status;
+// Device status area of this path (same four-word layout as the library's other status area: expired-wait
+// code, diagnostic flags, wait limit); zero when the module loads.  rf_fp8_gemm_static_status reads and clears it.
+static __device__ __align__(16) int g_static_status[rf::kStatusWords];
 
 struct StaticDevice {
-    bool ready = false;
+    std::atomic<bool> ready{false};
     float* scratch = nullptr;   // DEVICE address of g_static_scratch on this device
     int* status = nullptr;      // DEVICE address of g_static_status on this device
     int num_sms = 0;
@@ -41,9 +43,9 @@ int static_setup(StaticDevice** out) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= rf::kMaxDevices) return RF_ERR_CUDA;
     StaticDevice* sd = &g_static_dev[dev];
-    if (!sd->ready) {
+    if (!sd->ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_static_mu);
-        if (!sd->ready) {
+        if (!sd->ready.load(std::memory_order_relaxed)) {
             int major = 0, sms = 0;
             if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
                 cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
@@ -68,7 +70,7 @@ int static_setup(StaticDevice** out) {
             sd->scratch = static_cast<float*>(p);
             sd->status = static_cast<int*>(s);
             sd->num_sms = sms;
-            sd->ready = true;
+            sd->ready.store(true, std::memory_order_release);
         }
     }
     *out = sd;
@@ -124,6 +126,7 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
     p.c = static_cast<__nv_bfloat16*>(c);
     p.partial = splits > 1 ? sd->scratch : nullptr;   // every element of the slices is overwritten: nothing to clear
     p.status = sd->status;
+    p.launch_tag = rf::next_launch_tag();
     p.m = m; p.n = n; p.k = k;
     p.tiles_m = (m + rf::gemm_tile_rows(bn) - 1) / rf::gemm_tile_rows(bn);
     p.tiles_n = (n + rf::gemm_tile_cols(bn) - 1) / rf::gemm_tile_cols(bn);
@@ -133,12 +136,31 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
     p.n_dest = 1;
     p.c_col_offset = 0;
     p.dest_first = 0;
-    p.out_scale = 1.0f;
+    p.fnuz_flags = nullptr;
+    p.direct_store = 1;
     cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, nullptr, p, bn, sd->num_sms,
                                         reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {
         fprintf(stderr, "rf_fp8_gemm_static_scratch: launch failed: %s\n", cudaGetErrorString(e));
         return RF_ERR_CUDA;
+    }
+    return RF_OK;
+}
+
+// Reads and clears the status area of the allocation-free path (a copy from and to the symbol's device
+// address; no allocation).  Synchronises the device, like rf_device_status.
+extern "C" int rf_fp8_gemm_static_status(int* detail) {
+    StaticDevice* sd = nullptr;
+    int rc = static_setup(&sd);
+    if (rc != RF_OK) return rc;
+    int v[2] = {0, 0};
+    if (cudaDeviceSynchronize() != cudaSuccess) return RF_ERR_CUDA;
+    if (cudaMemcpy(v, sd->status, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return RF_ERR_CUDA;
+    if (detail) *detail = v[0] != 0 ? (v[0] & 0xFF) : v[1];
+    if (v[0] != 0 || v[1] != 0) {
+        const int zero[2] = {0, 0};
+        if (cudaMemcpy(sd->status, zero, sizeof(zero), cudaMemcpyHostToDevice) != cudaSuccess) return RF_ERR_CUDA;
+        return RF_ERR_DEVICE_TIMEOUT;
     }
     return RF_OK;
 }

@@ -13,13 +13,14 @@ constexpr int kBlockK = 128;
 
 bool shape_ok(int m, int n, int k) { return m > 0 && n > 0 && k > 0 && (n % 64) == 0 && (k % kBlockK) == 0; }
 
-// Tuning knob for experiments: RF_FP8_GEMM_BN=128|256|512 forces the tile configuration (512 = CTA pair).
+// Tuning knob for experiments: RF_FP8_GEMM_BN=128|256|384|512 forces the tile configuration (512 / 384 = CTA
+// pairs with 256 x 256 / 256 x 128 tiles).
 int forced_block_n() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("RF_FP8_GEMM_BN");
         v = e ? atoi(e) : 0;
-        if (v != 128 && v != 256 && v != 512) v = 0;
+        if (v != 128 && v != 256 && v != 384 && v != 512) v = 0;
     }
     return v;
 }
@@ -37,6 +38,17 @@ bool pair_config_enabled() {
     return v == 1;
 }
 
+// RF_FP8_GEMM_DIRECT_STORE=0 sends one-destination tiles through TMA stores instead of vector stores
+// (measurement knob; the N-split GEMM always uses TMA stores for its peer copies).
+bool direct_store_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RF_FP8_GEMM_DIRECT_STORE");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 struct GemmPlan {
     int block_n;
     int splits;
@@ -50,10 +62,10 @@ GemmPlan plan_for(int m, int n, int k, int num_sms, int bn, int forced_split) {
     const int tr = rf::gemm_tile_rows(bn), tc = rf::gemm_tile_cols(bn);
     const int tiles = ((m + tr - 1) / tr) * ((n + tc - 1) / tc);
     const int kb = k / kBlockK;
-    if (bn == 512) num_sms /= 2;     // work items go to CTA pairs
+    if (rf::gemm_is_pair(bn)) num_sms /= 2;     // work items go to CTA pairs
     // relative time of one K block of one work item, from in-kernel cycle counts
     // (128 x 128: ~620 cycles, 128 x 256: ~790, CTA pair 256 x 256: ~925)
-    const double tile_w = bn == 512 ? 1.5 : (bn == 256 ? 1.25 : 1.0);
+    const double tile_w = bn == 512 ? 1.5 : (bn == 256 ? 1.25 : (bn == 384 ? 0.8 : 1.0));
     GemmPlan best{bn, 1, 1e30};
     for (int s = 1; s <= 8; ++s) {
         if (forced_split > 0 && s != forced_split) continue;
@@ -115,7 +127,7 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     const int kb = k / kBlockK;
     if (split_k > kb) split_k = kb;
     GemmPlan plan = choose_plan(m, n, k, st->num_sms, split_k);
-    if (mn_major && plan.block_n == 512) plan = plan_for(m, n, k, st->num_sms, 256, split_k);
+    if (mn_major && rf::gemm_is_pair(plan.block_n)) plan = plan_for(m, n, k, st->num_sms, 256, split_k);
     const int bn = plan.block_n;
     const int splits = plan.splits;
 
@@ -167,6 +179,7 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     p.c = static_cast<__nv_bfloat16*>(c);
     p.partial = partial;
     p.status = st->status;
+    p.launch_tag = rf::next_launch_tag();
     p.m = m; p.n = n; p.k = k;
     p.tiles_m = (m + rf::gemm_tile_rows(bn) - 1) / rf::gemm_tile_rows(bn);
     p.tiles_n = (n + rf::gemm_tile_cols(bn) - 1) / rf::gemm_tile_cols(bn);
@@ -180,24 +193,44 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     }
     p.n_dest = n_dest;
     p.c_col_offset = col_offset;
-    p.out_scale = fnuz ? 0.25f : 1.0f;
-    if (fnuz) {
-        if (((size_t)m * k) % 16 != 0 || ((size_t)n * k) % 16 != 0) return RF_ERR_BAD_SHAPE;
-        if (rf::fp8_fnuz_check_launch(a, (size_t)m * k, st->status, st->num_sms, stream) != cudaSuccess ||
-            rf::fp8_fnuz_check_launch(b, (size_t)n * k, st->status, st->num_sms, stream) != cudaSuccess)
-            return RF_ERR_CUDA;
-    }
+    p.fnuz_flags = nullptr;
+    p.direct_store = direct_store_enabled() ? 1 : 0;
     p.dest_first = (n_dest > 1 && dest_n > 0 && n > 0) ? (col_offset / n) % n_dest : 0;   // = rank for an N-split
     rf::GemmDestMaps dests;
+    bool use_dests = false;
+    if (fnuz) {
+        // e4m3fnuz operands: one pass per operand writes the equal-valued e4m3fn bytes into library-owned
+        // scratch and flags operands that hold +-240 or NaN bytes; the kernel reads a flagged operand from
+        // its converted copy (maps in dests.m[0] / m[1]) and an unflagged one, exactly, from the caller's bytes.
+        const size_t a_bytes = (size_t)m * k, b_bytes = (size_t)n * k;
+        if (a_bytes % 16 != 0 || b_bytes % 16 != 0) return RF_ERR_BAD_SHAPE;
+        const size_t a_pad = (a_bytes + 255) / 256 * 256, b_pad = (b_bytes + 255) / 256 * 256;
+        char* conv = static_cast<char*>(rf::device_scratch(a_pad + b_pad + 256, rf::kScratchFnuz));
+        if (!conv) return RF_ERR_CUDA;
+        int* flags = reinterpret_cast<int*>(conv + a_pad + b_pad);
+        if (rf::fp8_fnuz_convert_launch(a, conv, a_bytes, flags, st->status, st->num_sms, stream) != cudaSuccess ||
+            rf::fp8_fnuz_convert_launch(b, conv + a_pad, b_bytes, flags + 1, st->status, st->num_sms, stream) !=
+                cudaSuccess)
+            return RF_ERR_CUDA;
+        if (!rf::encode_tma_2d(&dests.m[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, conv, (uint64_t)k, (uint64_t)m,
+                               (uint64_t)m, 128, 128, true) ||
+            !rf::encode_tma_2d(&dests.m[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, conv + a_pad, (uint64_t)k, (uint64_t)n,
+                               (uint64_t)n, 128, 128, true))
+            return RF_ERR_CUDA;
+        for (int i = 2; i < 8; ++i) dests.m[i] = dests.m[0];
+        p.fnuz_flags = flags;
+        use_dests = true;
+    }
     if (n_dest > 1) {
-        for (int i = 0; i < 8; ++i) {
-            void* base = dest_c[i < n_dest ? i : 0];
-            if (!rf::encode_tma_2d(&dests.m[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, (uint64_t)m,
+        for (int i = 0; i < n_dest; ++i) {
+            if (!rf::encode_tma_2d(&dests.m[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dest_c[i], (uint64_t)m,
                                    (uint64_t)dest_n, (uint64_t)dest_n * 2, 32, 64, true))
                 return RF_ERR_CUDA;
         }
+        for (int i = n_dest; i < 8; ++i) dests.m[i] = dests.m[0];
+        use_dests = true;
     }
-    cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, n_dest > 1 ? &dests : nullptr, p, bn, st->num_sms, stream,
+    cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, use_dests ? &dests : nullptr, p, bn, st->num_sms, stream,
                                         mn_major);
     if (e != cudaSuccess) {
         fprintf(stderr, "rf_b200: fp8 gemm launch failed: %s\n", cudaGetErrorString(e));
@@ -225,15 +258,24 @@ const char* rf_version(void) { return "rf_b200 0.1 sm_100a"; }
 int rf_device_status(int* detail) {
     rf::DeviceState* st = rf::device_state();
     if (!st) return RF_ERR_CUDA;
-    int v = 0;
+    int v[2] = {0, 0};
     if (cudaDeviceSynchronize() != cudaSuccess) return RF_ERR_CUDA;
-    if (cudaMemcpy(&v, st->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return RF_ERR_CUDA;
-    if (detail) *detail = v;
-    if (v != 0) {
-        cudaMemset(st->status, 0, sizeof(int));
+    if (cudaMemcpy(v, st->status, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return RF_ERR_CUDA;
+    // word 0: code of an expired wait (1-6); word 1: diagnostic flags (16, 32) that stopped nothing
+    if (detail) *detail = v[0] != 0 ? (v[0] & 0xFF) : v[1];
+    if (v[0] != 0 || v[1] != 0) {
+        cudaMemset(st->status, 0, sizeof(v));
         return RF_ERR_DEVICE_TIMEOUT;
     }
     return RF_OK;
+}
+
+int rf_set_wait_limit_ns(unsigned long long limit_ns) {
+    rf::DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    return cudaMemcpy(st->status + rf::kStatusLimitWord, &limit_ns, sizeof(limit_ns), cudaMemcpyHostToDevice) ==
+                   cudaSuccess
+               ? RF_OK : RF_ERR_CUDA;
 }
 
 int rf_fp8_gemm_get_plan(int m, int n, int k, int* block_n, int* split_k) {

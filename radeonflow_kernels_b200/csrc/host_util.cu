@@ -1,6 +1,7 @@
 #include "host_util.h"
 
 #include <cudaTypedefs.h>
+#include <atomic>
 #include <cstdio>
 #include <mutex>
 
@@ -37,16 +38,21 @@ DeviceState* device_state() {
         return nullptr;
     }
     st->num_sms = prop.multiProcessorCount;
-    if (cudaMalloc(&st->status, sizeof(int)) != cudaSuccess) return nullptr;
-    if (cudaMemset(st->status, 0, sizeof(int)) != cudaSuccess) return nullptr;
+    if (cudaMalloc(&st->status, sizeof(int) * kStatusWords) != cudaSuccess) return nullptr;
+    if (cudaMemset(st->status, 0, sizeof(int) * kStatusWords) != cudaSuccess) return nullptr;
     if (!load_encode()) return nullptr;
     st->init = true;
     return st;
 }
 
+int next_launch_tag() {
+    static std::atomic<unsigned> counter{0};
+    return (int)(counter.fetch_add(1, std::memory_order_relaxed) % (unsigned)kStatusTagMask) + 1;
+}
+
 void* device_scratch(size_t bytes, int slot) {
     DeviceState* st = device_state();
-    if (!st || slot < 0 || slot > 2) return nullptr;
+    if (!st || slot < 0 || slot >= kScratchSlots) return nullptr;
     if (bytes <= st->scratch_bytes[slot]) return st->scratch[slot];
     std::lock_guard<std::mutex> lock(g_mu);
     if (bytes <= st->scratch_bytes[slot]) return st->scratch[slot];

@@ -7,6 +7,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "status_words.h"
+
 namespace rf {
 
 constexpr int kMaxDevices = 64;
@@ -14,20 +16,26 @@ constexpr int kMaxDevices = 64;
 struct DeviceState {
     bool init = false;
     int num_sms = 0;
-    int* status = nullptr;          // device status word
-    void* scratch[3] = {nullptr, nullptr, nullptr};   // library-owned growable buffers, see ScratchSlot
-    size_t scratch_bytes[3] = {0, 0, 0};
+    int* status = nullptr;          // device status area: kStatusWords 32-bit words (layout in ptx.cuh)
+    void* scratch[4] = {nullptr, nullptr, nullptr, nullptr};   // library-owned growable buffers, see ScratchSlot
+    size_t scratch_bytes[4] = {0, 0, 0, 0};
 };
+
 
 enum ScratchSlot {
     kScratchGemm = 0,      // split-K slices of the FP8 GEMM
     kScratchMoeAux = 1,    // MoE tile lists and sort counters
     kScratchMoeWork = 2,   // MoE intermediates handed out by initialize_workspace
+    kScratchFnuz = 3,      // e4m3fn copies of e4m3fnuz operands (reference-format GEMM entry)
+    kScratchSlots = 4,
 };
 
 // State of the current device; initialises it on first use (allocates the
 // 4-byte status word).  Returns nullptr when a CUDA call fails.
 DeviceState* device_state();
+
+// A fresh tag (1 .. kStatusTagMask) for the next kernel launch that records expired waits.
+int next_launch_tag();
 
 // Library-owned buffer `slot` of at least `bytes` on the current device (grows by
 // freeing and re-allocating; synchronises the device when it grows).

@@ -32,25 +32,63 @@ int validate_params(const InputParams& q) {
 
 // ---------------------------------------------------------------- per-expert tensor-map cache --
 // Weights are static across calls, so the device array of tensor maps built for a set of weight
-// pointers is kept and found again by (pointers, shape).
+// pointers is kept and found again by (device, pointers, shape).  The cache holds 2048 sets by default (a
+// model of 100 MoE layers uses about 700) and evicts the least recently used one; a set used by the
+// grouped GEMM that is being enqueued is never evicted, and an evicted array is freed only after an event
+// recorded on the calling stream has completed, so a kernel that was enqueued with it can still read it.
+// (That, like the shared tile-list scratch, assumes what the reference also assumes: the MoE entry points
+// of one device are issued on one stream at a time.)  A miss costs one cudaMalloc and one blocking copy;
+// it happens at a layer's first call only.
 struct MapSet {
     int device;
     int rows, cols, box_rows, box_cols;
     std::vector<const void*> ptrs;
     CUtensorMap* dev_maps;
+    unsigned long long last_call;
 };
+struct RetiredMaps {
+    int device;
+    CUtensorMap* dev_maps;
+    cudaEvent_t done;
+};
+size_t g_max_map_sets = 2048;
 std::mutex g_map_mu;
 std::vector<MapSet> g_map_sets;
+std::vector<RetiredMaps> g_retired;
+unsigned long long g_map_call = 0;      // one number per grouped GEMM being enqueued
+
+void begin_map_call() {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    ++g_map_call;
+}
+
+// Frees retired arrays whose event has completed (never blocks).
+void reap_retired_locked(int dev) {
+    for (size_t i = 0; i < g_retired.size();) {
+        RetiredMaps& r = g_retired[i];
+        if (r.device == dev && cudaEventQuery(r.done) == cudaSuccess) {
+            cudaFree(r.dev_maps);
+            cudaEventDestroy(r.done);
+            g_retired.erase(g_retired.begin() + i);
+        } else {
+            ++i;
+        }
+    }
+    cudaGetLastError();     // cudaErrorNotReady from the queries is not an error
+}
 
 // Row-major fp16 matrices [rows, cols]; one map per pointer; returns a device array.
-const CUtensorMap* weight_maps(const void* const* ptrs, int count, int rows, int cols, int box_rows, int box_cols) {
+const CUtensorMap* weight_maps(const void* const* ptrs, int count, int rows, int cols, int box_rows, int box_cols,
+                               cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lock(g_map_mu);
-    for (const MapSet& m : g_map_sets) {
+    for (MapSet& m : g_map_sets) {
         if (m.device == dev && m.rows == rows && m.cols == cols && m.box_rows == box_rows && m.box_cols == box_cols &&
-            (int)m.ptrs.size() == count && memcmp(m.ptrs.data(), ptrs, sizeof(void*) * count) == 0)
+            (int)m.ptrs.size() == count && memcmp(m.ptrs.data(), ptrs, sizeof(void*) * count) == 0) {
+            m.last_call = g_map_call;
             return m.dev_maps;
+        }
     }
     std::vector<CUtensorMap> host(count);
     for (int i = 0; i < count; ++i) {
@@ -59,18 +97,34 @@ const CUtensorMap* weight_maps(const void* const* ptrs, int count, int rows, int
                                (uint64_t)cols * 2, (uint32_t)box_rows, (uint32_t)box_cols, true))
             return nullptr;
     }
+    reap_retired_locked(dev);
     MapSet m;
     m.device = dev;
     m.rows = rows; m.cols = cols; m.box_rows = box_rows; m.box_cols = box_cols;
     m.ptrs.assign(ptrs, ptrs + count);
     m.dev_maps = nullptr;
+    m.last_call = g_map_call;
     if (cudaMalloc(&m.dev_maps, sizeof(CUtensorMap) * count) != cudaSuccess) return nullptr;
-    if (cudaMemcpy(m.dev_maps, host.data(), sizeof(CUtensorMap) * count, cudaMemcpyHostToDevice) != cudaSuccess)
+    if (cudaMemcpy(m.dev_maps, host.data(), sizeof(CUtensorMap) * count, cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaFree(m.dev_maps);
         return nullptr;
-    if (g_map_sets.size() >= 64) {   // bounded: drop the oldest set
-        cudaDeviceSynchronize();
-        cudaFree(g_map_sets.front().dev_maps);
-        g_map_sets.erase(g_map_sets.begin());
+    }
+    if (g_map_sets.size() >= g_max_map_sets) {
+        // least recently used set that the call in progress does not use
+        size_t victim = g_map_sets.size();
+        for (size_t i = 0; i < g_map_sets.size(); ++i)
+            if (g_map_sets[i].last_call != g_map_call &&
+                (victim == g_map_sets.size() || g_map_sets[i].last_call < g_map_sets[victim].last_call))
+                victim = i;
+        if (victim < g_map_sets.size()) {
+            RetiredMaps r{g_map_sets[victim].device, g_map_sets[victim].dev_maps, nullptr};
+            // kernels already enqueued on this stream may still read the array: free it after they are done
+            if (cudaEventCreateWithFlags(&r.done, cudaEventDisableTiming) == cudaSuccess &&
+                cudaEventRecord(r.done, stream) == cudaSuccess)
+                g_retired.push_back(r);
+            // (if the event could not be made the array is leaked rather than freed under a running kernel)
+            g_map_sets.erase(g_map_sets.begin() + victim);
+        }
     }
     g_map_sets.push_back(m);
     return m.dev_maps;
@@ -159,11 +213,12 @@ int grouped_gemm(int mode, const void* x, int n_rows, const void* const* w_host,
     if (n_rows <= 0) return RF_OK;
     const CUtensorMap* maps;
     const CUtensorMap* maps2 = nullptr;
+    begin_map_call();
     if (mode == rf::kMoeGemmRouter) {
-        maps = weight_maps(w_host, 1, n_out, k, 256, 64);            // [N, K] row-major, box 256 rows x 64 K
+        maps = weight_maps(w_host, 1, n_out, k, 256, 64, stream);            // [N, K] row-major, box 256 rows x 64 K
     } else {
-        maps = weight_maps(w_host, n_groups, k, n_out, 64, 64);      // [K, N] row-major, box 64 K-rows x 64 N
-        if (mode == rf::kMoeGemmSwiglu) maps2 = weight_maps(w2_host, n_groups, k, n_out, 64, 64);
+        maps = weight_maps(w_host, n_groups, k, n_out, 64, 64, stream);      // [K, N] row-major, box 64 K-rows x 64 N
+        if (mode == rf::kMoeGemmSwiglu) maps2 = weight_maps(w2_host, n_groups, k, n_out, 64, 64, stream);
     }
     if (!maps || (mode == rf::kMoeGemmSwiglu && !maps2)) return RF_ERR_CUDA;
     CUtensorMap ta, to;
@@ -198,6 +253,7 @@ int grouped_gemm(int mode, const void* x, int n_rows, const void* const* w_host,
     if (scatter_dst) p.scatter_dst = *scatter_dst;
     else memset(&p.scatter_dst, 0, sizeof p.scatter_dst);
     p.status = st->status;
+    p.launch_tag = rf::next_launch_tag();
     if (rf::moe_gemm_launch(mode, ta, to, p, st->num_sms, stream) != cudaSuccess) return RF_ERR_CUDA;
     return RF_OK;
 }
@@ -298,6 +354,13 @@ int moe_layer(MoEInputRaw* in, bool compute_router, const float* router_bias, cu
 }  // namespace
 
 extern "C" {
+
+int rf_moe_set_map_cache_sets(int max_sets) {
+    if (max_sets < 4) return RF_ERR_BAD_SHAPE;      // one grouped GEMM pins up to two sets
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    g_max_map_sets = (size_t)max_sets;
+    return RF_OK;
+}
 
 int run_topk(MoEInputRaw* input, rf_stream_t stream, PerfMetrics* metrics) {
     return moe_layer(input, false, nullptr, reinterpret_cast<cudaStream_t>(stream), metrics);

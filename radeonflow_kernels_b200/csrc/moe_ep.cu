@@ -14,8 +14,8 @@ namespace rf {
 namespace {
 
 __global__ void __launch_bounds__(1024)
-ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_experts, int* __restrict__ send_base,
-                 int* __restrict__ recv_offsets) {
+ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_experts, int capacity,
+                 int* __restrict__ send_base, int* __restrict__ recv_offsets, int* __restrict__ status) {
     __shared__ int tot[1024];
     const int e = threadIdx.x;
     const int per = n_experts / world;
@@ -44,6 +44,12 @@ ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_
     if (e <= per) {
         int off = 0;
         for (int j = 0; j < e; ++j) off += tot[rank * per + j];
+        // Rows beyond the receive capacity are never written by the senders (ep_dispatch_kernel drops them):
+        // the expert row ranges are clipped to the capacity and the overflow is reported.
+        if (off > capacity) {
+            if (e == per) atomicOr(status + kStatusDiagWord, (int)kDiagEpOverflow);
+            off = capacity;
+        }
         recv_offsets[e] = off;
     }
 }
@@ -55,8 +61,9 @@ __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted_experts,
                    const int* __restrict__ permuted_rows, const int* __restrict__ first_token_offset,
                    const int* __restrict__ send_base, int n_tokens, int n_pairs, int vec_per_row,
-                   int experts_per_rank, int rank, int world, PeerPtrs recv_x, PeerPtrs recv_meta, int with_meta,
-                   int* __restrict__ pair_rank, int* __restrict__ pair_row) {
+                   int experts_per_rank, int rank, int world, int capacity, PeerPtrs recv_x, PeerPtrs recv_meta,
+                   int with_meta, int* __restrict__ pair_rank, int* __restrict__ pair_row, uint4* __restrict__ drop_fill,
+                   int* __restrict__ status) {
     // Pairs are sorted by expert, hence by destination rank.  Every source starts with a different
     // destination (rank+1, rank+2, ...), so at any moment the senders target different GPUs instead of
     // all writing into the same one.
@@ -67,6 +74,20 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted
         const int e = __ldg(permuted_experts + p);
         const int q = e / experts_per_rank;
         const int row = __ldg(send_base + e) + (p - __ldg(first_token_offset + e));
+        if (row >= capacity) {
+            // the owner's receive buffer is full: the row is dropped (its result will be missing), never
+            // written past the allocation on another GPU; -1 marks the pair for the pulling combine, and
+            // where results are pushed home the pair's result row is zeroed here instead
+            if (drop_fill != nullptr)
+                for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += 256)
+                    drop_fill[(size_t)p * vec_per_row + v0] = make_uint4(0u, 0u, 0u, 0u);
+            if (threadIdx.x == 0) {
+                pair_rank[p] = -1;
+                pair_row[p] = 0;
+                atomicOr(status + kStatusDiagWord, (int)kDiagEpOverflow);
+            }
+            continue;
+        }
         const int tok = __ldg(permuted_rows + p) % n_tokens;
         const uint4* src = x + (size_t)tok * vec_per_row;
         uint4* dst = static_cast<uint4*>(pick_peer(recv_x, q)) + (size_t)row * vec_per_row;
@@ -96,8 +117,10 @@ ep_combine_kernel(PeerPtrs y, const uint4* __restrict__ shared_out, const int* _
     __shared__ float w_s[8];
     if (threadIdx.x < top_k) {
         const int p = rev[threadIdx.x * n_tokens + t];
-        src_s[threadIdx.x] = static_cast<const uint4*>(pick_peer(y, pair_rank[p])) + (size_t)pair_row[p] * vec_per_row;
-        w_s[threadIdx.x] = __half2float(weights[p]);
+        const int q = pair_rank[p];
+        // a pair dropped by the dispatch (receive buffer full) contributes nothing
+        src_s[threadIdx.x] = static_cast<const uint4*>(pick_peer(y, q < 0 ? 0 : q)) + (size_t)pair_row[p] * vec_per_row;
+        w_s[threadIdx.x] = q < 0 ? 0.f : __half2float(weights[p]);
     }
     __syncthreads();
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
@@ -161,14 +184,15 @@ add_rows_kernel(uint4* __restrict__ out, const uint4* __restrict__ add, size_t n
 // rank can never be overtaken by two epochs.  The wait is bounded: on expiry the status word is set
 // and the kernel returns.
 __global__ void __launch_bounds__(256)
-ep_rendezvous_kernel(PeerPtrs sync, const int* __restrict__ counts, int n_counts, int rank, int world, int epoch,
-                     int* status) {
+ep_rendezvous_kernel(PeerPtrs sync, const int* __restrict__ counts, int n_counts, int from_offsets, int rank,
+                     int world, int epoch, int* status) {
     if (counts != nullptr) {
         for (int i = threadIdx.x; i < n_counts * world; i += blockDim.x) {
             const int peer = i / n_counts;
             const int j = i - peer * n_counts;
             int* area = static_cast<int*>(pick_peer(sync, peer));
-            area[8 + rank * n_counts + j] = counts[j];
+            // `counts` is either the values themselves or n_counts + 1 ascending offsets (first_token_offset)
+            area[8 + rank * n_counts + j] = from_offsets ? counts[j + 1] - counts[j] : counts[j];
         }
     }
     __threadfence_system();          // the counts (and every earlier peer store of this stream) before the flag
@@ -179,9 +203,10 @@ ep_rendezvous_kernel(PeerPtrs sync, const int* __restrict__ counts, int n_counts
         *theirs = epoch;
         volatile int* mine = static_cast<int*>(pick_peer(sync, rank)) + peer;
         const unsigned long long t0 = globaltimer_ns();
+        const unsigned long long limit = wait_limit_ns(status);
         unsigned spins = 0;
         while (*mine < epoch) {
-            if ((++spins & 0x3ff) == 0 && globaltimer_ns() - t0 > kWaitTimeoutNs) {
+            if ((++spins & 0x3ff) == 0 && globaltimer_ns() - t0 > limit) {
                 atomicCAS(status, 0, kErrSchedWait);
                 break;
             }
@@ -192,9 +217,10 @@ ep_rendezvous_kernel(PeerPtrs sync, const int* __restrict__ counts, int n_counts
 
 }  // namespace
 
-cudaError_t moe_ep_rendezvous_launch(const PeerPtrs& sync, const int* counts, int n_counts, int rank, int world,
-                                     int epoch, int* status, cudaStream_t stream) {
-    ep_rendezvous_kernel<<<1, 256, 0, stream>>>(sync, counts, n_counts, rank, world, epoch, status);
+cudaError_t moe_ep_rendezvous_launch(const PeerPtrs& sync, const int* counts, int n_counts, bool from_offsets,
+                                     int rank, int world, int epoch, int* status, cudaStream_t stream) {
+    ep_rendezvous_kernel<<<1, 256, 0, stream>>>(sync, counts, n_counts, from_offsets ? 1 : 0, rank, world, epoch,
+                                                status);
     return cudaGetLastError();
 }
 
@@ -209,26 +235,28 @@ cudaError_t moe_add_rows_launch(void* out, const void* add, size_t n_elems, int 
     return cudaGetLastError();
 }
 
-cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int n_experts, int* send_base,
-                                 int* recv_offsets, cudaStream_t stream) {
-    ep_layout_kernel<<<1, 1024, 0, stream>>>(counts_all, rank, world, n_experts, send_base, recv_offsets);
+cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int n_experts, int capacity,
+                                 int* send_base, int* recv_offsets, int* status, cudaStream_t stream) {
+    ep_layout_kernel<<<1, 1024, 0, stream>>>(counts_all, rank, world, n_experts, capacity, send_base, recv_offsets,
+                                             status);
     return cudaGetLastError();
 }
 
 cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, const int* permuted_rows,
                                    const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs,
-                                   int row_bytes, int experts_per_rank, int rank, int world, const PeerPtrs& recv_x,
-                                   const PeerPtrs* recv_meta, int* pair_rank, int* pair_row, int num_sms,
-                                   cudaStream_t stream) {
+                                   int row_bytes, int experts_per_rank, int rank, int world, int capacity,
+                                   const PeerPtrs& recv_x, const PeerPtrs* recv_meta, int* pair_rank, int* pair_row,
+                                   void* drop_fill, int* status, int num_sms, int max_blocks, cudaStream_t stream) {
     const int vec = row_bytes / 16;
     if (n_pairs == 0) return cudaSuccess;
-    int blocks = num_sms * 8;
+    int blocks = max_blocks > 0 ? max_blocks : num_sms * 8;
     if (blocks > n_pairs) blocks = n_pairs;
     ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(x), permuted_experts,
                                                              permuted_rows, first_token_offset, send_base, n_tokens,
-                                                             n_pairs, vec, experts_per_rank, rank, world, recv_x,
-                                                             recv_meta ? *recv_meta : recv_x, recv_meta ? 1 : 0,
-                                                             pair_rank, pair_row);
+                                                             n_pairs, vec, experts_per_rank, rank, world, capacity,
+                                                             recv_x, recv_meta ? *recv_meta : recv_x,
+                                                             recv_meta ? 1 : 0, pair_rank, pair_row,
+                                                             static_cast<uint4*>(drop_fill), status);
     return cudaGetLastError();
 }
 

@@ -124,7 +124,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             for (int ks = 0; ks < k_steps; ++ks, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1, p.status, kErrProducerWait));
+                ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1, p.status, kErrProducerWait, p.launch_tag));
                 if (!ok) break;
                 if (elect_one()) {
                     mbar_expect_tx(full_bar(s), STAGE_BYTES);
@@ -156,13 +156,13 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tcount) {
             const int buf = tcount & 1;
             const uint32_t bph = (tcount >> 1) & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(buf), bph ^ 1, p.status, kErrMmaWaitTmem));
+            ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(buf), bph ^ 1, p.status, kErrMmaWaitTmem, p.launch_tag));
             if (!ok) break;
             const uint32_t d = tmem_base + buf * BN;
             for (int ks = 0; ks < k_steps; ++ks, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, kErrMmaWaitFull));
+                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, kErrMmaWaitFull, p.launch_tag));
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t sa = smem_base + s * STAGE_BYTES;
@@ -202,7 +202,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const int row_end = __ldg(p.group_offsets + grp + 1);
             const int buf = tcount & 1;
             const uint32_t bph = (tcount >> 1) & 1;
-            if (!mbar_wait(tmem_full_bar(buf), bph, p.status, kErrEpilogueWait)) { ok = false; break; }
+            if (!mbar_wait(tmem_full_bar(buf), bph, p.status, kErrEpilogueWait, p.launch_tag)) { ok = false; break; }
             tc_fence_after();
 
             const int slab_row0 = row0 + quad * 32;

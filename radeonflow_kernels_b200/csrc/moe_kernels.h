@@ -40,18 +40,23 @@ __device__ __forceinline__ void* pick_peer(const PeerPtrs& pp, int q) {
 // counts_all [world][n_experts] (row s = pairs per global expert on source rank s).  Writes
 //   send_base[e]      row, inside the owner rank's receive buffer, of this rank's first pair for expert e
 //   recv_offsets[j]   j = 0..n_experts/world: row range of local expert j in this rank's receive buffer
-cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int n_experts, int* send_base,
-                                 int* recv_offsets, cudaStream_t stream);
+// Row ranges are clipped to `capacity` (rows of the receive buffers); an overflow ORs kDiagEpOverflow into
+// the diagnostics word of `status`.
+cudaError_t moe_ep_layout_launch(const int* counts_all, int rank, int world, int n_experts, int capacity,
+                                 int* send_base, int* recv_offsets, int* status, cudaStream_t stream);
 // Copies the token row of every local (token, expert) pair into the owner rank's receive buffer
 // (peer stores) and records where it went (pair_rank, pair_row).  With `recv_meta` != nullptr it also
 // writes, beside every row it sends, the return address of the row's result: (this rank << 28) | p, p = the
 // pair's position in this rank's expert-sorted order (kEpMetaSlotBits bits).
+// A pair whose destination row is >= `capacity` is not sent: pair_rank = -1, kDiagEpOverflow is raised, and
+// with `drop_fill` != nullptr (this rank's fp16 [n_pairs, row] result matrix) its result row is zeroed.
+// `max_blocks` > 0 caps the grid (to leave SMs to a GEMM running beside it).
 constexpr int kEpMetaSlotBits = 28;
 cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, const int* permuted_rows,
                                    const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs,
-                                   int row_bytes, int experts_per_rank, int rank, int world, const PeerPtrs& recv_x,
-                                   const PeerPtrs* recv_meta, int* pair_rank, int* pair_row, int num_sms,
-                                   cudaStream_t stream);
+                                   int row_bytes, int experts_per_rank, int rank, int world, int capacity,
+                                   const PeerPtrs& recv_x, const PeerPtrs* recv_meta, int* pair_rank, int* pair_row,
+                                   void* drop_fill, int* status, int num_sms, int max_blocks, cudaStream_t stream);
 // out[t] = fp16(sum_i w_i * Y_{rank_i}[row_i] + shared[t]) with Y rows read from the owner ranks (peer loads).
 cudaError_t moe_ep_combine_launch(const PeerPtrs& y, const void* shared_out, const int* rev, const void* weights,
                                   const int* pair_rank, const int* pair_row, int n_tokens, int top_k, int row_bytes,
@@ -65,8 +70,9 @@ cudaError_t moe_add_rows_launch(void* out, const void* add, size_t n_elems, int 
 // Each rank stores `epoch` into its slot on every peer and waits (bounded) until its own slots hold
 // `epoch`; with `counts` != nullptr it first publishes its n_counts values into row `rank` of every
 // peer's gather area.  One launch per rank, every rank on its own GPU.
-cudaError_t moe_ep_rendezvous_launch(const PeerPtrs& sync, const int* counts, int n_counts, int rank, int world,
-                                     int epoch, int* status, cudaStream_t stream);
+// `from_offsets`: `counts` holds n_counts + 1 ascending offsets and their differences are published.
+cudaError_t moe_ep_rendezvous_launch(const PeerPtrs& sync, const int* counts, int n_counts, bool from_offsets,
+                                     int rank, int world, int epoch, int* status, cudaStream_t stream);
 
 // ---- grouped fp16 GEMM (moe_gemm.cu)
 enum MoeGemmMode {
@@ -96,7 +102,8 @@ struct MoeGemmParams {
     int n_out;                  // output columns
     int k;                      // reduction length (multiple of 64)
     int tma_store;              // 1: full 32-row slabs leave through the output tensor map
-    int* status;
+    int* status;                // device status area (status_words.h)
+    int launch_tag;             // tag recorded with an expired wait
 };
 
 cudaError_t moe_gemm_launch(int mode, const CUtensorMap& tma_a, const CUtensorMap& tma_out, const MoeGemmParams& p,

@@ -62,31 +62,33 @@ int rf_moe_ep_rendezvous(void* const* sync_all, const int* counts_dev, int n_cou
     for (int i = 0; i < 8; ++i) pp.p[i] = sync_all[i < world ? i : 0];
     for (int i = 0; i < world; ++i)
         if (!pp.p[i] || ((uintptr_t)pp.p[i] & 15)) return RF_ERR_NULL_POINTER;
-    return rf::moe_ep_rendezvous_launch(pp, counts_dev, counts_dev ? n_counts : 0, rank, world, epoch, st->status,
-                                        reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+    return rf::moe_ep_rendezvous_launch(pp, counts_dev, counts_dev ? n_counts : 0, false, rank, world, epoch,
+                                        st->status, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
                ? RF_OK : RF_ERR_CUDA;
 }
 
-int rf_moe_ep_layout(const int* counts_all_dev, int rank, int world, int n_experts, int* send_base_dev,
+int rf_moe_ep_layout(const int* counts_all_dev, int rank, int world, int n_experts, int capacity, int* send_base_dev,
                      int* recv_offsets_dev, rf_stream_t stream) {
     if (!counts_all_dev || !send_base_dev || !recv_offsets_dev) return RF_ERR_NULL_POINTER;
     if (world < 1 || world > 8 || rank < 0 || rank >= world || n_experts < world || n_experts > 1024 ||
-        n_experts % world != 0)
+        n_experts % world != 0 || capacity < 1)
         return RF_ERR_BAD_SHAPE;
-    return rf::moe_ep_layout_launch(counts_all_dev, rank, world, n_experts, send_base_dev, recv_offsets_dev,
-                                    reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+    rf::DeviceState* st = rf::device_state();
+    if (!st) return RF_ERR_CUDA;
+    return rf::moe_ep_layout_launch(counts_all_dev, rank, world, n_experts, capacity, send_base_dev, recv_offsets_dev,
+                                    st->status, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
                ? RF_OK : RF_ERR_CUDA;
 }
 
 int rf_moe_ep_dispatch(const void* x, const int* permuted_experts, const int* permuted_rows,
                        const int* first_token_offset, const int* send_base, int n_tokens, int n_pairs, int d_hidden,
-                       int n_experts, int rank, int world, void* const* recv_x_all, void* const* recv_meta_all,
-                       int* pair_rank, int* pair_row, rf_stream_t stream) {
+                       int n_experts, int rank, int world, int capacity, void* const* recv_x_all,
+                       void* const* recv_meta_all, int* pair_rank, int* pair_row, void* drop_fill, rf_stream_t stream) {
     if (!x || !permuted_experts || !permuted_rows || !first_token_offset || !send_base || !recv_x_all || !pair_rank ||
         !pair_row)
         return RF_ERR_NULL_POINTER;
     if (world < 1 || world > 8 || rank < 0 || rank >= world || n_experts % world != 0 || d_hidden <= 0 ||
-        d_hidden % 8 != 0 || n_tokens <= 0 || n_pairs < 0)
+        d_hidden % 8 != 0 || n_tokens <= 0 || n_pairs < 0 || capacity < 1)
         return RF_ERR_BAD_SHAPE;
     rf::DeviceState* st = rf::device_state();
     if (!st) return RF_ERR_CUDA;
@@ -102,9 +104,9 @@ int rf_moe_ep_dispatch(const void* x, const int* permuted_experts, const int* pe
             if (!pm.p[i] || ((uintptr_t)pm.p[i] & 3)) return RF_ERR_NULL_POINTER;
     }
     return rf::moe_ep_dispatch_launch(x, permuted_experts, permuted_rows, first_token_offset, send_base, n_tokens,
-                                      n_pairs, d_hidden * 2, n_experts / world, rank, world, pp,
-                                      recv_meta_all ? &pm : nullptr, pair_rank, pair_row, st->num_sms,
-                                      reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+                                      n_pairs, d_hidden * 2, n_experts / world, rank, world, capacity, pp,
+                                      recv_meta_all ? &pm : nullptr, pair_rank, pair_row, drop_fill, st->status,
+                                      st->num_sms, 0, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
                ? RF_OK : RF_ERR_CUDA;
 }
 

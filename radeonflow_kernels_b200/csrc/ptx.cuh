@@ -2,8 +2,8 @@
 // mbarrier, TMA (cp.async.bulk.tensor), tcgen05 (alloc / mma / commit / ld) and
 // the shared-memory matrix descriptors that tcgen05.mma consumes.
 //
-// Every wait is bounded: a wait that does not complete within kWaitTimeoutNs
-// records an error code in a global status word and returns false, and the
+// Every wait is bounded: a wait that does not complete within the wait limit
+// records an error code in the device status area and returns false, and the
 // caller unwinds to the kernel's tear-down (TMEM is freed, the CTA exits).
 #pragma once
 
@@ -13,11 +13,13 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include "status_words.h"
+
 namespace rf {
 
-constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // default wait limit: 2 s
 
-// Error codes written to the device status word (first writer wins).
+// Error codes written to status word 0 (first writer wins).
 enum DeviceError : int {
     kErrNone = 0,
     kErrProducerWait = 1,   // TMA producer timed out waiting for a free stage
@@ -26,7 +28,11 @@ enum DeviceError : int {
     kErrEpilogueWait = 4,   // epilogue timed out waiting for an accumulator
     kErrSchedWait = 5,      // tile-list / inter-CTA flag wait timed out
     kErrStoreWait = 6,      // epilogue timed out waiting for a staging buffer
-    kErrFnuzByte = 16,      // an e4m3fnuz input byte has no e4m3fn counterpart (0x80, 0x7F, 0xFF)
+};
+// Flags OR-ed into status word 1.
+enum DeviceDiag : int {
+    kDiagFnuzByte = 16,     // an e4m3fnuz operand holds +-240 (0x7F / 0xFF): it was computed from converted bytes
+    kDiagEpOverflow = 32,   // expert-parallel dispatch: rows beyond the receive capacity were dropped
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -77,17 +83,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false (after recording `code` in *status) on timeout
-// or when another role already recorded an error.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+// Bounded wait.  Returns false on timeout, after recording `code` (with the launch's tag in the upper bits)
+// in status word 0 if no earlier code is there, or when another role OF THE SAME LAUNCH already recorded one:
+// a kernel that lost one role unwinds at once, while a code left by an earlier launch that nobody has read
+// yet does not make later launches give up their waits.
+__device__ __forceinline__ unsigned long long wait_limit_ns(const int* status) {
+    const unsigned long long v =
+        *reinterpret_cast<const volatile unsigned long long*>(status + kStatusLimitWord);
+    return v ? v : kWaitTimeoutNs;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code, int tag) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 0xffu) == 0) {
-            if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-            if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
-                atomicCAS(status, 0, code);
+            const int seen = *reinterpret_cast<volatile int*>(status);
+            if (seen != 0 && (seen >> kStatusTagShift) == tag) return false;
+            if (globaltimer_ns() - t0 > wait_limit_ns(status)) {
+                atomicCAS(status, 0, code | (tag << kStatusTagShift));
                 return false;
             }
         }
@@ -301,6 +315,44 @@ __device__ __forceinline__ void tmem_ld32_async(uint32_t taddr, float (&v)[32]) 
         : "r"(taddr)
         : "memory");
 }
+// In-place loads: the destination registers are named as read-write operands, so every earlier use of
+// the staging buffer is ordered before the load and the buffer keeps its registers (a fresh set of 32 or 64
+// live registers per load is more than the epilogue's register budget holds).
+// 64 consecutive columns in one instruction (v0 = columns 0-31, v1 = 32-63); valid after tmem_ld_fence2.
+__device__ __forceinline__ void tmem_ld64_async(uint32_t taddr, float (&v0)[32], float (&v1)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v0);
+    uint32_t* q = reinterpret_cast<uint32_t*>(v1);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]),
+          "+r"(q[0]), "+r"(q[1]), "+r"(q[2]), "+r"(q[3]), "+r"(q[4]), "+r"(q[5]), "+r"(q[6]), "+r"(q[7]),
+          "+r"(q[8]), "+r"(q[9]), "+r"(q[10]), "+r"(q[11]), "+r"(q[12]), "+r"(q[13]), "+r"(q[14]), "+r"(q[15]),
+          "+r"(q[16]), "+r"(q[17]), "+r"(q[18]), "+r"(q[19]), "+r"(q[20]), "+r"(q[21]), "+r"(q[22]), "+r"(q[23]),
+          "+r"(q[24]), "+r"(q[25]), "+r"(q[26]), "+r"(q[27]), "+r"(q[28]), "+r"(q[29]), "+r"(q[30]), "+r"(q[31])
+        : "r"(taddr)
+        : "memory");
+}
+// 32 consecutive columns into a staging buffer that is being reused; valid after tmem_ld_fence / _fence2.
+__device__ __forceinline__ void tmem_ld32_async_inplace(uint32_t taddr, float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
 // tcgen05.wait::ld that also names the destination registers as read-write
 // operands, so no use of them can be scheduled above the wait.
 __device__ __forceinline__ void tmem_ld_fence(float (&v)[32]) {
@@ -313,6 +365,24 @@ __device__ __forceinline__ void tmem_ld_fence(float (&v)[32]) {
           "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
         :
         : "memory");
+}
+
+// Names 32 more registers as read-write without emitting an instruction: placed directly after
+// tmem_ld_fence(v0) it extends that wait to a second staging buffer.
+__device__ __forceinline__ void reg_fence(float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        ""
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_fence2(float (&v0)[32], float (&v1)[32]) {
+    tmem_ld_fence(v0);
+    reg_fence(v1);
 }
 
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of

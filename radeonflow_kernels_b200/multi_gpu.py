@@ -3,10 +3,11 @@
 * ``fp8_gemm_nsplit`` - the large FP8 GEMM split along N; every rank's epilogue TMA-stores its
   column slab of C into every rank's full C over NVLink (the all-gather is part of the kernel).
 * ``ExpertParallelMoE`` - the MoE layer with experts sharded ``E / world`` per rank; tokens are
-  dispatched by peer stores into the owner's receive buffer and expert outputs are combined by
-  peer loads.  The per-step control traffic (a [world, E] count all-gather and two barriers) also
-  goes through peer memory (``rf_moe_ep_rendezvous``); ``torch.distributed`` (NCCL) is used at set-up
-  to exchange the IPC handles, and by the N-split GEMM for its completion barrier.
+  dispatched by peer stores into the owner's receive buffer and expert outputs come home by peer
+  stores from the second expert GEMM's epilogue (or are pulled by the combine).  The per-step control
+  traffic (a [world, E] count all-gather and two barriers) also goes through peer memory; the step is
+  sequenced by the library's C++ ``RfMoeEp`` object.  ``torch.distributed`` (NCCL) is used at set-up to
+  exchange the IPC handles, and by the N-split GEMM for its completion barrier.
 
 The reference is single-GPU (no collective call anywhere in it); these are additions on top of
 its operator boundary, built from the same C-ABI stage entry points.
@@ -161,15 +162,21 @@ def fp8_gemm_nsplit(a, b_shard, a_scale, b_scale_shard, c_buf: PeerBuffer, m: in
 class ExpertParallelMoE:
     """MoE layer with experts sharded over the ranks of ``group`` (expert e on rank e // (E/world)).
 
+    A thin owner of the library's ``RfMoeEp`` object: the per-step sequence (router GEMM, top-k, sort,
+    count exchange, dispatch beside the shared expert, routed experts, results home, combine), its
+    buffers, streams, events and epochs all live in C++ (``csrc/moe_ep_api.cu``); ``forward`` is one
+    call.  ``torch.distributed`` is used here only to exchange the IPC handles at set-up and for the
+    barriers around set-up and tear-down.
+
     weights: 'router.weight' [E, d] and 'shared_experts.{0,1,2}.weight' replicated on every rank;
     'experts.{j}.{0,1,2}.weight' for the LOCAL experts j = 0..E/world-1 (global id rank*E/world + j).
     Every rank feeds its own ``n_tokens`` tokens.  ``capacity`` = rows the receive buffers hold
-    (default: worst case, every pair of every rank lands here).
+    (default: worst case, every pair of every rank lands here); rows beyond it are dropped and reported
+    (``_lib`` status detail 32), never written.
 
     ``push_results`` (default): the experts' second GEMM stores every output row from its epilogue straight
-    into the GPU that owns the token (`rf_moe_grouped_gemm_scatter`), so the transfer back overlaps the GEMM
-    tile by tile and the final combine is local.  False: the outputs stay on the expert's GPU and the
-    combine kernel pulls them over NVLink (`rf_moe_ep_combine`).
+    into the GPU that owns the token, so the transfer back overlaps the GEMM tile by tile and the final
+    combine is local.  False: the outputs stay on the expert's GPU and the combine pulls them over NVLink.
     """
 
     def __init__(self, config, weights, n_tokens: int, device, group=None, capacity=None, router_bias=None,
@@ -182,170 +189,107 @@ class ExpertParallelMoE:
         self.K = int(config["n_experts_per_token"])
         self.d = int(config["d_hidden"])
         self.f = int(config["d_expert"])
-        self.fs = self.f * int(config["n_shared_experts"])
         if self.E % self.world:
             raise ValueError("n_routed_experts must be divisible by the number of ranks")
+        if capacity is not None and int(capacity) < 1:
+            raise ValueError("capacity must be at least one row")
         self.E_loc = self.E // self.world
         self.T = int(n_tokens)
-        self.n_pairs = self.T * self.K
-        self.capacity = int(capacity) if capacity else self.n_pairs * self.world
-        self.weights = weights
+        self.weights = weights              # keeps the tensors alive: the library holds their addresses
         self.router_bias = router_bias
-        # on one GPU nothing travels: the plain second GEMM (TMA stores) plus the gathering combine is faster
-        self.push_results = bool(push_results) and self.world > 1
-        self.trace = None           # set to [] to time the stages of the next forward
-        dev, T, K, E, d, f = self.device, self.T, self.K, self.E, self.d, self.f
-        i32, f16 = torch.int32, torch.float16
-        e = lambda shape, dt: torch.empty(shape, dtype=dt, device=dev)
-        self.scores = e((T, E), f16)
-        self.idx = e((T, K), i32)
-        self.gate_w = e((T, K), f16)
-        self.source_rows = e((T * K,), i32)
-        self.perm_experts = e((T * K,), i32)
-        self.perm_rows = e((T * K,), i32)
-        self.first = e((E + 1,), i32)
-        self.rev = e((T * K,), i32)
-        self.exp_w = e((T * K,), f16)
-        self.pair_rank = e((T * K,), i32)
-        self.pair_row = e((T * K,), i32)
-        self.counts = e((E,), i32)
-        self.send_base = e((E,), i32)
-        self.recv_offsets = e((self.E_loc + 1,), i32)
-        self.single_offsets = torch.tensor([0, T], dtype=i32, device=dev)
-        self.sh1 = e((T, self.fs), f16)
-        self.sh2 = e((T, d), f16)
-        self.h = e((self.capacity, f), f16)
-        self.out = e((T, d), f16)
-        self.flag = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.out = torch.empty((self.T, self.d), dtype=torch.float16, device=self.device)
         L = _lib.lib()
-        self.sort_scratch = e((max(16, L.rf_moe_permute_scratch_bytes(T * K, E)),), torch.uint8)
-        self.side_stream = torch.cuda.Stream(device=dev)
-        self.ev_ready = torch.cuda.Event()
-        self.ev_sent = torch.cuda.Event()
-        # sync area: 8 arrival flags + the [world, E] count matrix, zeroed before the first epoch
-        self.sync = PeerBuffer(4 * (8 + self.world * E), dev, group)
-        self.sync.tensor(torch.int32, (8 + self.world * E,)).zero_()
-        self.counts_all = self.sync.tensor(torch.int32, (8 + self.world * E,))[8:]
-        self.epoch = 0
-        torch.cuda.synchronize()
-        if self.world > 1:
-            dist.barrier(group=group)           # every rank's sync area is zero before anyone raises a flag
-        self.recv_x = PeerBuffer(self.capacity * d * 2, dev, group)
-        if self.push_results:
-            # results come home by peer stores: one row per local (token, expert) pair, expert-sorted order
-            self.y = PeerBuffer(max(16, self.n_pairs * d * 2), dev, group)
-            self.recv_meta = PeerBuffer(4 * self.capacity, dev, group)
-        else:
-            self.y = PeerBuffer(self.capacity * d * 2, dev, group)
-            self.recv_meta = None
+        cfg = _lib.RfMoeEpConfig(self.T, self.d, self.f, self.E, self.K, int(config["n_shared_experts"]), self.rank,
+                                 self.world, int(capacity) if capacity else 0, 1 if push_results else 0)
+        ep = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(L.rf_moe_ep_create(ctypes.byref(cfg), ctypes.byref(ep)), "rf_moe_ep_create")
+            self._ep = ep
+            if self.world > 1:
+                mine = (ctypes.c_ubyte * _lib.RF_MOE_EP_HANDLE_BYTES)()
+                _lib.check(L.rf_moe_ep_handles(ep, mine), "rf_moe_ep_handles")
+                t = torch.tensor(list(mine), dtype=torch.uint8, device=self.device)
+                allh = torch.empty(self.world * _lib.RF_MOE_EP_HANDLE_BYTES, dtype=torch.uint8, device=self.device)
+                dist.all_gather_into_tensor(allh, t, group=group)
+                blob = (ctypes.c_ubyte * (self.world * _lib.RF_MOE_EP_HANDLE_BYTES))(*allh.cpu().tolist())
+                _lib.check(L.rf_moe_ep_connect(ep, blob), "rf_moe_ep_connect")
 
-        def ptr_array(tensors):
-            arr = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
-            return arr
-        self._w_gate = ptr_array([weights[f"experts.{j}.0.weight"] for j in range(self.E_loc)])
-        self._w_up = ptr_array([weights[f"experts.{j}.1.weight"] for j in range(self.E_loc)])
-        self._w_down = ptr_array([weights[f"experts.{j}.2.weight"] for j in range(self.E_loc)])
-        self._s_gate = ptr_array([weights["shared_experts.0.weight"]])
-        self._s_up = ptr_array([weights["shared_experts.1.weight"]])
-        self._s_down = ptr_array([weights["shared_experts.2.weight"]])
+            def ptr_array(names):
+                return (ctypes.c_void_p * len(names))(*[weights[n].data_ptr() for n in names])
+            self._w = [ptr_array([f"experts.{j}.{q}.weight" for j in range(self.E_loc)]) for q in range(3)]
+            _lib.check(L.rf_moe_ep_set_weights(
+                ep, weights["router.weight"].data_ptr(), router_bias.data_ptr() if router_bias is not None else None,
+                self._w[0], self._w[1], self._w[2], weights["shared_experts.0.weight"].data_ptr(),
+                weights["shared_experts.1.weight"].data_ptr(), weights["shared_experts.2.weight"].data_ptr()),
+                "rf_moe_ep_set_weights")
+            torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(group=group)       # every rank's sync area is zero and mapped before anyone raises a flag
 
     def forward(self, x):
         """x: fp16 [T, d] local tokens -> fp16 [T, d]."""
-        L = _lib.lib()
-        T, K, E, d, f = self.T, self.K, self.E, self.d, self.f
-        s = _stream()
-        chk = _lib.check
-        self._mark("start")
-        bias = self.router_bias.data_ptr() if self.router_bias is not None else None
-        chk(L.rf_moe_router_gemm(x.data_ptr(), self.weights["router.weight"].data_ptr(), bias, T, E, d,
-                                 self.scores.data_ptr(), s), "rf_moe_router_gemm")
-        chk(L.rf_moe_topk(self.scores.data_ptr(), T, E, K, self.idx.data_ptr(), self.gate_w.data_ptr(),
-                          self.source_rows.data_ptr(), s), "rf_moe_topk")
-        chk(L.rf_moe_permute(self.idx.data_ptr(), self.source_rows.data_ptr(), self.gate_w.data_ptr(), T, E, K,
-                             self.perm_experts.data_ptr(), self.perm_rows.data_ptr(), self.first.data_ptr(),
-                             self.rev.data_ptr(), self.exp_w.data_ptr(), self.sort_scratch.data_ptr(), s),
-            "rf_moe_permute")
-        # pair counts per global expert, all-gathered through peer memory; the rendezvous also orders this
-        # step after every rank's previous combine (its reads of our y buffer)
-        torch.sub(self.first[1:], self.first[:-1], out=self.counts)
-        self._rendezvous(self.counts.data_ptr(), E)
-        self._mark("route+counts")
-        chk(L.rf_moe_ep_layout(self.counts_all.data_ptr(), self.rank, self.world, E, self.send_base.data_ptr(),
-                               self.recv_offsets.data_ptr(), s), "rf_moe_ep_layout")
-        # Dispatch runs on a side stream; the shared expert, which needs no exchange, runs on the main
-        # stream at the same time (the copy kernel's blocks need no shared memory and co-reside with
-        # the GEMM's CTAs), hiding the NVLink transfer.
-        main = torch.cuda.current_stream()
-        self.ev_ready.record(main)
-        self.side_stream.wait_event(self.ev_ready)
-        side = ctypes.c_void_p(self.side_stream.cuda_stream)
-        chk(L.rf_moe_ep_dispatch(x.data_ptr(), self.perm_experts.data_ptr(), self.perm_rows.data_ptr(),
-                                 self.first.data_ptr(), self.send_base.data_ptr(), T, T * K, d, E, self.rank, self.world,
-                                 self.recv_x.ptr_array, self.recv_meta.ptr_array if self.push_results else None,
-                                 self.pair_rank.data_ptr(), self.pair_row.data_ptr(), side),
-            "rf_moe_ep_dispatch")
-        self.ev_sent.record(self.side_stream)
-        chk(L.rf_moe_grouped_gemm(x.data_ptr(), T, self._s_gate, self._s_up, self.single_offsets.data_ptr(), 1,
-                                  self.fs, d, self.sh1.data_ptr(), s), "shared fc1")
-        chk(L.rf_moe_grouped_gemm(self.sh1.data_ptr(), T, self._s_down, None, self.single_offsets.data_ptr(), 1, d,
-                                  self.fs, self.sh2.data_ptr(), s), "shared fc2")
-        main.wait_event(self.ev_sent)
-        self._mark("dispatch+shared")
-        self._rendezvous(None, 0)                       # every rank's dispatch has landed
-        self._mark("barrier1")
-        chk(L.rf_moe_grouped_gemm(self.recv_x.local_ptr, self.capacity, self._w_gate, self._w_up,
-                                  self.recv_offsets.data_ptr(), self.E_loc, f, d, self.h.data_ptr(), s), "routed fc1")
-        self._mark("routed fc1")
-        if self.push_results:
-            chk(L.rf_moe_grouped_gemm_scatter(self.h.data_ptr(), self.capacity, self._w_down,
-                                              self.recv_offsets.data_ptr(), self.E_loc, d, f,
-                                              self.recv_meta.local_ptr, self.y.ptr_array, self.world, s),
-                "routed fc2 + return")
-        else:
-            chk(L.rf_moe_grouped_gemm(self.h.data_ptr(), self.capacity, self._w_down, None,
-                                      self.recv_offsets.data_ptr(), self.E_loc, d, f, self.y.local_ptr, s),
-                "routed fc2")
-        self._mark("routed fc2")
-        self._rendezvous(None, 0)                       # every rank's expert outputs are complete (and home)
-        self._mark("barrier2")
-        if self.push_results:
-            chk(L.rf_moe_combine(self.y.local_ptr, self.sh2.data_ptr(), self.rev.data_ptr(), self.exp_w.data_ptr(),
-                                 T, K, d, self.out.data_ptr(), s), "rf_moe_combine")
-            self._mark("combine")
-            return self.out
-        # (Running the shared expert's second GEMM concurrently with this combine and adding its rows
-        # afterwards with rf_moe_add_rows was measured: no gain on 8 GPUs, and one more fp16 rounding.)
-        chk(L.rf_moe_ep_combine(self.y.ptr_array, self.sh2.data_ptr(), self.rev.data_ptr(), self.exp_w.data_ptr(),
-                                self.pair_rank.data_ptr(), self.pair_row.data_ptr(), T, K, d, self.world,
-                                self.out.data_ptr(), s), "rf_moe_ep_combine")
-        self._mark("combine")
+        _lib.check(_lib.lib().rf_moe_ep_forward(self._ep, x.data_ptr(), self.out.data_ptr(), _stream()),
+                   "rf_moe_ep_forward")
         return self.out
 
-    def _mark(self, name):
-        """Stage timing aid: when `self.trace` is a list, records (name, CUDA event) pairs on the main stream."""
-        if self.trace is not None:
-            ev = torch.cuda.Event(enable_timing=True)
-            ev.record(torch.cuda.current_stream())
-            self.trace.append((name, ev))
+    def set_trace(self, on: bool):
+        _lib.check(_lib.lib().rf_moe_ep_set_option(self._ep, _lib.RF_MOE_EP_OPT_TRACE, 1 if on else 0), "trace")
+
+    def set_dispatch_blocks(self, blocks: int):
+        _lib.check(_lib.lib().rf_moe_ep_set_option(self._ep, _lib.RF_MOE_EP_OPT_DISPATCH_BLOCKS, int(blocks)),
+                   "dispatch blocks")
 
     def stage_times_ms(self):
-        """Milliseconds between consecutive marks of the last traced forward (synchronises)."""
-        torch.cuda.synchronize()
-        t = self.trace or []
-        return [(t[i][0], t[i - 1][1].elapsed_time(t[i][1])) for i in range(1, len(t))]
+        """(name, milliseconds) of the stages of the last traced forward (synchronises)."""
+        ms = (ctypes.c_float * 16)()
+        names = (ctypes.c_char_p * 16)()
+        n = _lib.lib().rf_moe_ep_stage_times(self._ep, ms, names, 16)
+        return [(names[i].decode(), float(ms[i])) for i in range(n)]
 
-    def _rendezvous(self, counts_ptr, n_counts):
-        self.epoch += 1
-        _lib.check(_lib.lib().rf_moe_ep_rendezvous(self.sync.ptr_array, counts_ptr, n_counts, self.rank, self.world,
-                                                   self.epoch, _stream()), "rf_moe_ep_rendezvous")
+    def _buffer(self, which, dtype, shape):
+        p, nb = ctypes.c_void_p(), ctypes.c_size_t()
+        _lib.check(_lib.lib().rf_moe_ep_buffer(self._ep, which, ctypes.byref(p), ctypes.byref(nb)), "rf_moe_ep_buffer")
+        flat = torch.as_tensor(_RawCuda(p.value, nb.value), device=self.device)
+        return flat.view(dtype).view(*shape)
+
+    @property
+    def scores(self):
+        return self._buffer(_lib.RF_MOE_EP_BUF_SCORES, torch.float16, (self.T, self.E))
+
+    @property
+    def idx(self):
+        return self._buffer(_lib.RF_MOE_EP_BUF_INDEX, torch.int32, (self.T, self.K))
+
+    @property
+    def counts_all(self):
+        return self._buffer(_lib.RF_MOE_EP_BUF_COUNTS_ALL, torch.int32, (self.world * self.E,))
+
+    @property
+    def send_base(self):
+        return self._buffer(_lib.RF_MOE_EP_BUF_SEND_BASE, torch.int32, (self.E,))
+
+    @property
+    def recv_offsets(self):
+        return self._buffer(_lib.RF_MOE_EP_BUF_RECV_OFFSETS, torch.int32, (self.E_loc + 1,))
+
+    @property
+    def pair_rank(self):
+        return self._buffer(_lib.RF_MOE_EP_BUF_PAIR_RANK, torch.int32, (self.T * self.K,))
 
     def received_rows(self) -> int:
         """Rows this rank's experts processed in the last forward (synchronises)."""
         return int(self.recv_offsets[-1].item())
 
     def close(self):
-        self.recv_x.close()
-        self.y.close()
-        if self.recv_meta is not None:
-            self.recv_meta.close()
-        self.sync.close()
+        if self._ep is None:
+            return
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(group=self.group)      # nobody still reads or writes a peer's buffers
+            L.rf_moe_ep_disconnect(self._ep)
+            if self.world > 1:
+                dist.barrier(group=self.group)      # every mapping of my buffers is closed before I free them
+            L.rf_moe_ep_destroy(self._ep)
+            self._ep = None

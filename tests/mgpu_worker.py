@@ -98,6 +98,27 @@ def main():
     assert np.array_equal(layer.recv_offsets.cpu().numpy(), ro)
     assert layer.received_rows() == int(counts_all[:, rank * e_loc:(rank + 1) * e_loc].sum())
     layer.close()
+
+    # ---- 3. receive buffers smaller than the traffic: rows beyond the capacity are dropped and reported,
+    # never written; tokens that lost no pair still get the oracle's result
+    need = int(counts_all[:, rank * e_loc:(rank + 1) * e_loc].sum())
+    cap = max(8, min(int(counts_all[:, q * e_loc:(q + 1) * e_loc].sum()) for q in range(world)) // 2)
+    small = mg.ExpertParallelMoE(cfg, dw, T_loc, dev, router_bias=torch.from_numpy(bias).to(dev), capacity=cap)
+    out_small = small.forward(x_loc).clone()
+    torch.cuda.synchronize()
+    kept = (small.pair_rank.cpu().numpy() >= 0)
+    assert small.received_rows() == min(need, cap)
+    assert G.device_status() == 32, "the overflow must be reported"
+    assert torch.isfinite(out_small.float()).all()
+    # pair p (expert-sorted order) belongs to token perm_rows[p] % T_loc; recover it from the oracle's permutation
+    ref_loc = om.moe_stages(x[0, rank * T_loc:(rank + 1) * T_loc], w, E, K, logits16=logits_loc)
+    tok_of_pair = ref_loc["permuted_rows"] % T_loc
+    whole = np.ones(T_loc, dtype=bool)
+    whole[tok_of_pair[~kept]] = False
+    if whole.any():
+        okw, nbw, mxw = om.check(out_small.cpu().numpy()[whole], ref["final_output"][rank * T_loc:(rank + 1) * T_loc][whole])
+        assert okw, f"rank {rank}: tokens that lost no pair differ ({nbw} elements, max {mxw})"
+    small.close()
     print(f"MGPU OK rank={rank} world={world} gemm_maxerr={mx:.3g}", flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -86,10 +86,28 @@ def test_expert_parallel_entries_validate_on_the_host(rf_lib):
     # dispatch: experts not divisible by the ranks, rank out of range, missing pointer
     d = lambda **kw: rf_lib.rf_moe_ep_dispatch(
         kw.get("x", p16), p16, p16, p16, p16, 64, 256, 128, kw.get("e", 8), kw.get("rank", 0), kw.get("world", 2),
-        ptrs, kw.get("meta", ptrs), p16, p16, None)
+        kw.get("cap", 512), ptrs, kw.get("meta", ptrs), p16, p16, None, None)
     assert d(e=7) == 1 and d(rank=2) == 1 and d(world=9) == 1
+    assert d(cap=0) == 1                                                   # a receive buffer holds at least one row
     assert d(x=None) == 2
-    assert rf_lib.rf_moe_ep_layout(p16, 0, 3, 8, p16, p16, None) == 1      # 8 experts over 3 ranks
+    assert rf_lib.rf_moe_ep_layout(p16, 0, 3, 8, 64, p16, p16, None) == 1      # 8 experts over 3 ranks
+    assert rf_lib.rf_moe_ep_layout(p16, 0, 2, 8, 0, p16, p16, None) == 1       # capacity < 1
+
+
+def test_expert_parallel_object_validates_its_configuration(rf_lib):
+    """rf_moe_ep_create refuses bad configurations before it touches a device."""
+    mk = lambda **kw: _lib.RfMoeEpConfig(*[kw.get(n, v) for n, v in (
+        ("n_tokens", 64), ("d_hidden", 128), ("d_expert", 64), ("n_routed_experts", 8), ("n_experts_per_token", 2),
+        ("n_shared_experts", 1), ("rank", 0), ("world", 2), ("capacity", 0), ("push_results", 1))])
+    out = ctypes.c_void_p()
+    create = lambda cfg: rf_lib.rf_moe_ep_create(ctypes.byref(cfg), ctypes.byref(out))
+    assert create(mk(world=9)) == 1 and create(mk(rank=2)) == 1
+    assert create(mk(n_tokens=0)) == 1 and create(mk(d_hidden=100)) == 1
+    assert create(mk(n_routed_experts=6)) == 7            # power of two, divisible by the ranks
+    assert create(mk(n_experts_per_token=9)) == 7
+    assert create(mk(capacity=-1)) == 1
+    assert rf_lib.rf_moe_ep_create(None, ctypes.byref(out)) == 2
+    assert rf_lib.rf_moe_ep_forward(None, None, None, None) == 2
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -32,7 +32,8 @@ def test_algorithmic_work_formulas():
 
 def test_reference_arm_prints_one_json_line_and_only_on_rank_0():
     env = dict(os.environ, OMP_NUM_THREADS="4")
-    cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"]
+    cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+           "--shapes", "1024x512x7168,1024x4096x512"]
     quiet = subprocess.run(cmd, env=dict(env, RANK="1", WORLD_SIZE="2"), capture_output=True, text=True, timeout=300)
     assert quiet.returncode == 0 and quiet.stdout.strip() == ""
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
@@ -42,6 +43,13 @@ def test_reference_arm_prints_one_json_line_and_only_on_rank_0():
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["metric"] == "fp8_blockscaled_gemm_tflops" and d["unit"] == "TFLOP/s"
     assert d["higher_is_better"] is True and d["value"] > 0 and d["steps"] == 1
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["value"] == d["value"] and d["cpu_baseline"]["cores"] >= 1
+    # the reference's own ref_kernel where oracle/_ref exists (made by oracle/make_ref.py), else the numpy restatement
+    have_ref = os.path.exists(os.path.join(ROOT, "oracle", "_ref", "scripts", "problems", "gemm", "reference.py"))
+    assert d["cpu_baseline"]["kind"] == ("reference" if have_ref else "port")
+    assert d["cpu_baseline"]["value"] == d["value"]
+    # the arm sets its own thread count: torchrun's OMP_NUM_THREADS=1 (4 in this test) must not shrink it
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+    b = _bench_module()
+    assert d["config"] == b.sweep_config(1, "1024x512x7168,1024x4096x512")
     assert d["e2e"] == {"value": d["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["gpu_launches"] == 0

@@ -185,9 +185,10 @@ def test_perf_metrics_are_filled(rf_lib):
     assert pm.count >= 1 and pm.entries[0].time > 0 and pm.entries[0].gflops > 0
 
 
-def test_cta_pair_configuration_matches_oracle():
-    """The cta_group::2 configuration (256 x 256 tile per 2-CTA cluster) is selected per process by an
-    environment variable, so it runs in a child process."""
+@pytest.mark.parametrize("block_n", ["512", "384"])
+def test_cta_pair_configuration_matches_oracle(block_n):
+    """The cta_group::2 configurations (256 x 256 and 256 x 128 tiles per 2-CTA cluster) are selected per
+    process by an environment variable, so they run in a child process."""
     import subprocess
     import sys
     code = r'''
@@ -207,7 +208,7 @@ for (m, n, k, split, dist) in [(300, 576, 1024, 1, "randn"), (1024, 1536, 7168, 
     assert ok, (m, n, k, nbad, mx)
 print("PAIR OK")
 '''
-    env = dict(os.environ, RF_FP8_GEMM_BN="512", RF_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    env = dict(os.environ, RF_FP8_GEMM_BN=block_n, RF_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "PAIR OK" in res.stdout, (res.stdout + res.stderr)[-3000:]
 
@@ -282,20 +283,85 @@ def test_custom_kernel_takes_the_reference_generators_tuple():
     assert_close(c.view(torch.uint16).cpu().numpy(), exp)
 
 
-@pytest.mark.parametrize("bad,where", [(0x80, "a"), (0x7F, "b"), (0xFF, "a")])
-def test_fnuz_entry_reports_bytes_it_cannot_read(rf_lib, bad, where):
-    m, n, k = 64, 128, 256
-    a, b, a_s, b_s = o.generate_input_fnuz(m, n, k, 31)
-    (a if where == "a" else b)[5, 77] = bad
+def _fnuz_call(rf_lib, a, b, a_s, b_s):
     from tests.helpers import to_dev
+    m, n, k = a.shape[0], b.shape[0], a.shape[1]
     da, db = to_dev(np.ascontiguousarray(a.T)), to_dev(np.ascontiguousarray(b.T))
     das, dbs = to_dev(np.ascontiguousarray(a_s.T)), to_dev(np.ascontiguousarray(b_s.T))
-    c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda:0")
+    full, c = canary_output(m, n)
     st = rf_lib.rf_fp8_gemm_colmajor_fnuz(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(),
                                           c.data_ptr(), m, n, k, None, 0, None)
     assert st == 0
-    assert G.device_status() == 16          # recorded, and cleared by the read
+    torch.cuda.synchronize()
+    assert canary_intact(full, m, n)
+    return c.view(torch.uint16).cpu().numpy()
+
+
+@pytest.mark.parametrize("bad,where", [(0x7F, "b"), (0xFF, "a"), (0x7F, "a")])
+def test_fnuz_entry_computes_the_largest_magnitudes(rf_lib, bad, where):
+    """+-240 (0x7F / 0xFF) has no e4m3fn reading at twice its value: the flagged operand is computed from its
+    converted copy, the result still matches the fnuz oracle, the note (16) is reported once, and the GEMM
+    that follows is unaffected."""
+    m, n, k = 64, 128, 256
+    a, b, a_s, b_s = o.generate_input_fnuz(m, n, k, 31)
+    (a if where == "a" else b)[5, 77] = bad
+    got = _fnuz_call(rf_lib, a, b, a_s, b_s)
+    assert_close(got, o.fp8_gemm_fnuz(a, b, a_s, b_s))
+    assert G.device_status() == 16          # a note, reported once and cleared by the read
     assert G.device_status() == 0
+    a2, b2, a_s2, b_s2 = o.generate_input(96, 192, 384, 5, "randn")
+    full, c = canary_output(96, 192)
+    G.fp8_mm(*gemm_device_inputs(a2, b2, a_s2, b_s2), c)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0 and canary_intact(full, 96, 192)
+    assert_close(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a2, b2, a_s2, b_s2))
+
+
+@pytest.mark.parametrize("m,n,k,seed", [(64, 128, 256, 41), (96, 320, 512, 42), (1040, 576, 1024, 43)])
+def test_fnuz_entry_on_amax_scaled_blocks(rf_lib, m, n, k, seed):
+    """Block-quantised data (scale = amax / 240) puts +-240 into practically every 128-block of BOTH operands and
+    many values below 2^-6 beside it; the result must still match the fnuz oracle."""
+    rng = np.random.default_rng(seed)
+    kb, nb = k // 128, (n + 127) // 128
+
+    def quantise(x, blocks_r):
+        """scale[r, kb] = amax of the block / 240; bytes = e4m3fnuz(x / scale): the block's largest element is +-240"""
+        q = np.empty(x.shape, dtype=np.uint8)
+        sc = np.empty((-(-x.shape[0] // blocks_r), kb), dtype=np.float32)
+        for r in range(sc.shape[0]):
+            for c in range(kb):
+                blk = x[r * blocks_r:(r + 1) * blocks_r, c * 128:(c + 1) * 128]
+                sc[r, c] = np.abs(blk).max() / np.float32(240.0)
+                q[r * blocks_r:(r + 1) * blocks_r, c * 128:(c + 1) * 128] = o.encode_e4m3fnuz(blk / sc[r, c])
+        return q, sc
+    a, a_s = quantise(rng.standard_normal((m, k), dtype=np.float32), 1)
+    b, b_s = quantise(rng.standard_normal((n, k), dtype=np.float32), 128)
+    b_s = b_s[:nb]
+    assert ((a & 0x7F) == 0x7F).sum() >= m * kb and ((b & 0x7F) == 0x7F).sum() >= nb * kb
+    # every magnitude below 2^-6 (bytes 0x01-0x0F, the ones the conversion has to round) in both operands
+    small = (rng.integers(1, 16, size=a[::3, 1::5].shape) | (rng.integers(0, 2, size=a[::3, 1::5].shape) << 7))
+    a[::3, 1::5] = small.astype(np.uint8)
+    b[1::2, 2::7] = (rng.integers(1, 16, size=b[1::2, 2::7].shape)).astype(np.uint8)
+    assert not (a == 0x80).any() and not (b == 0x80).any()
+    got = _fnuz_call(rf_lib, a, b, a_s, b_s)
+    assert_close(got, o.fp8_gemm_fnuz(a, b, a_s, b_s))
+    assert G.device_status() == 16 and G.device_status() == 0
+
+
+def test_fnuz_nan_byte_stays_nan(rf_lib):
+    """0x80 is NaN in e4m3fnuz (the reference's output would be NaN in that row); read as e4m3fn it would be
+    -0.  The converted copy keeps it NaN: row 5 of C is NaN, every other row matches the oracle."""
+    m, n, k = 64, 128, 256
+    a, b, a_s, b_s = o.generate_input_fnuz(m, n, k, 31)
+    a[5, 77] = 0x80
+    got = _fnuz_call(rf_lib, a, b, a_s, b_s).view(np.uint16)
+    is_nan = (got & 0x7FFF) > 0x7F80
+    assert is_nan[5].all() and not np.delete(is_nan, 5, axis=0).any()
+    a_ok = a.copy()
+    a_ok[5, 77] = 0
+    exp = o.fp8_gemm_fnuz(a_ok, b, a_s, b_s)
+    assert_close(np.delete(got, 5, axis=0), np.delete(exp, 5, axis=0))
+    assert G.device_status() == 16 and G.device_status() == 0
 
 
 @pytest.mark.parametrize("path", GOLDEN_FNUZ, ids=[os.path.basename(p) for p in GOLDEN_FNUZ])

@@ -38,6 +38,10 @@ def run_both(rf_lib, m, n, k, split, seed):
     assert np.array_equal(got, ref), "static-scratch variant differs from rf_fp8_gemm"
     ok, nbad, mx = o.check(got, o.fp8_gemm(a, b, a_s, b_s))
     assert ok, (nbad, mx)
+    # the path's own status area: nothing expired, and reading it allocates nothing and leaves it clear
+    import ctypes
+    detail = ctypes.c_int(-1)
+    assert rf_lib.rf_fp8_gemm_static_status(ctypes.byref(detail)) == 0 and detail.value == 0
 
 
 def test_two_calls_in_a_row_match_the_ordinary_entry_point(rf_lib):
