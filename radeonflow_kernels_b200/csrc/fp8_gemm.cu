@@ -84,6 +84,7 @@ struct GemmCfg {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemBufs = 512 / BN;                // accumulator buffers in flight
     static constexpr int kTmemCols = kTmemBufs * BN;          // all 512 TMEM columns
+    // full / empty / peer-full per stage, full / empty per accumulator buffer, the TMEM address slot (16 bytes)
     static constexpr int kBarBytes = (3 * STAGES + 2 * kTmemBufs) * 8 + 16;
     static constexpr int kSlabBytes = 32 * 128;               // one slab: 32 rows x 128 B, swizzled
     static constexpr int kSlabs = SLABS;                      // slabs per epilogue warp
@@ -354,35 +355,47 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #endif
         // (in a CTA pair tmem_empty lives in the leader CTA, the only MMA issuer; both CTAs arrive on it
         // through the cluster window)
-        for (int w = unit; w < total_work && ok; w += unit_stride) {
-            // (the tile's coordinates are decoded again after the K loop for the store: nothing but the
-            // accumulators, the staging buffers and the scale queue should stay live across that loop)
-            int kb0, kb1;
-            long long as_off, bs_off;      // element offsets of this thread's scale rows
-            {
-                const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
-                kb0 = (int)((long long)kb_total * t.split / p.splits);
-                kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
-                const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
-                const int row = cta_m_blk * BM + row_in_tile;
-                const int col0 = t.n_blk * BN + grp * CPT;
-                as_off = (long long)(row < p.m ? row : 0) * p.as_row_stride;
-                bs_off = (long long)(col0 < p.n ? (col0 >> 7) : 0) * p.bs_row_stride;
+        // K-major scale tables have unit stride along K (a compile-time fact the address arithmetic of the
+        // prefetch queue depends on); only the reference's [k/128][m] tables stride by m
+        const int as_ks = Cfg::kMnMajor ? (int)p.as_k_stride : 1;
+        const int bs_ks = Cfg::kMnMajor ? (int)p.bs_k_stride : 1;
+        // out_scale (reference-layout configurations only): 1 for e4m3fn bytes.  e4m3fnuz bytes read as
+        // e4m3fn are twice their value, so each operand that is consumed unconverted contributes 1/2; an
+        // operand read from its converted copy (true values) contributes 1.  A power of two commutes
+        // exactly with every rounding of the fp32 accumulation.
+        float out_scale = 1.0f;
+        if (Cfg::kMnMajor && p.fnuz_flags != nullptr)
+            out_scale = (p.fnuz_flags[0] != 0 ? 1.0f : 0.5f) * (p.fnuz_flags[1] != 0 ? 1.0f : 0.5f);
+        // Scale loads run PF K blocks ahead of their use so their latency (L2 or HBM) never sits on the
+        // per-K-block critical path.  (Requesting a tile's first scales before the previous tile is stored was
+        // measured: no gain on long K, 8 % slower on K <= 512.)
+#if RF_EPI_WIDE
+        constexpr int PF = 3;
+#else
+        constexpr int PF = 4;
+#endif
+        float qa[PF], qb[PF];
+        int kb0 = 0, kb1 = 0;
+        const float* as_row = p.a_scale;
+        const float* bs_row = p.b_scale;
+        auto begin_tile = [&](int wi) {
+            const TileCoord t = decode_work(wi, p.tiles_m, p.tiles_n, p.splits);
+            kb0 = (int)((long long)kb_total * t.split / p.splits);
+            kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
+            const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
+            const int row = cta_m_blk * BM + row_in_tile;
+            const int col0 = t.n_blk * BN + grp * CPT;
+            as_row = p.a_scale + (long long)(row < p.m ? row : 0) * p.as_row_stride;
+            bs_row = p.b_scale + (long long)(col0 < p.n ? (col0 >> 7) : 0) * p.bs_row_stride;
+#pragma unroll
+            for (int d = 0; d < PF; ++d) {
+                const int kk = min(kb0 + d, kb1 - 1);
+                qa[d] = __ldg(as_row + kk * as_ks);
+                qb[d] = __ldg(bs_row + kk * bs_ks);
             }
-            const float* as_row = p.a_scale + as_off;
-            const float* bs_row = p.b_scale + bs_off;
-            // K-major scale tables have unit stride along K (a compile-time fact the address arithmetic
-            // of the prefetch queue depends on); only the reference's [k/128][m] tables stride by m
-            const int as_ks = Cfg::kMnMajor ? (int)p.as_k_stride : 1;
-            const int bs_ks = Cfg::kMnMajor ? (int)p.bs_k_stride : 1;
-            // out_scale (reference-layout configurations only): 1 for e4m3fn bytes.  e4m3fnuz bytes read as
-            // e4m3fn are twice their value, so each operand that is consumed unconverted contributes 1/2; an
-            // operand read from its converted copy (true values) contributes 1.  A power of two commutes
-            // exactly with every rounding of the fp32 accumulation.
-            float out_scale = 1.0f;
-            if (Cfg::kMnMajor && p.fnuz_flags != nullptr)
-                out_scale = (p.fnuz_flags[0] != 0 ? 1.0f : 0.5f) * (p.fnuz_flags[1] != 0 ? 1.0f : 0.5f);
-
+        };
+        for (int w = unit; w < total_work && ok; w += unit_stride) {
+            begin_tile(w);
             float2 acc[CPT / 2];
 #pragma unroll
             for (int j = 0; j < CPT / 2; ++j) acc[j] = make_float2(0.f, 0.f);
@@ -391,19 +404,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             float v[2][32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[0][j] = v[1][j] = 0.f;
-            constexpr int PF = 3;
-#else
-            constexpr int PF = 4;
 #endif
-            // Scale loads run PF K blocks ahead of their use so their latency
-            // (L2 or HBM) never sits on the per-K-block critical path.
-            float qa[PF], qb[PF];
-#pragma unroll
-            for (int d = 0; d < PF; ++d) {
-                const int kk = min(kb0 + d, kb1 - 1);
-                qa[d] = __ldg(as_row + kk * as_ks);
-                qb[d] = __ldg(bs_row + kk * bs_ks);
-            }
 #if RF_EPI_WIDE
 #pragma unroll 1
 #else
@@ -489,8 +490,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #endif
             }
             if (!ok) break;
-            // Tile store.  Each warp transposes its 32 rows x 128 bytes through its own swizzled shared-memory
-            // slab so that global memory is written in whole 128-byte row segments.
+            // Tile store: each warp stages its 32 rows x 128 bytes in its own swizzled shared-memory slab, so
+            // that global memory is written in whole 128-byte row segments.
             {
                 constexpr int SL = Cfg::kSlabs;
                 const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
@@ -498,63 +499,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 const int col0 = t.n_blk * BN + grp * CPT;
                 const uint32_t slab0 = slab_base + ew * SL * Cfg::kSlabBytes;
                 const int slab_row0 = cta_m_blk * BM + quad * 32;
-                if (p.direct_store && p.n_dest <= 1) {
-                    // Default for one destination: the warp reads the slab back row-segment-wise (8 lanes per
-                    // 128-byte segment) and stores it with ordinary vector stores.  Unlike a TMA store the slab
-                    // is free again as soon as those loads have returned, so the 2 (fp32 slices: 4) chunks of a
-                    // tile follow each other without waiting for an asynchronous read of the slab; the MMA warps
-                    // sit idle behind this phase once both accumulator buffers of the next tile are full.
-                    const uint32_t my_row = slab0 + lane * 128;
-                    const int c8 = lane & 7, rsub = lane >> 3;
-                    if (p.splits == 1) {
-#pragma unroll
-                        for (int ch = 0; ch < CPT / 64; ++ch) {
-                            if (col0 + ch * 64 >= p.n) break;
-                            __syncwarp();            // every lane has read the previous chunk out of the slab
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int a0 = ch * 32 + j * 4;
-                                st_shared_v4(my_row + ((j ^ (lane & 7)) << 4),
-                                             pack_bf16x2(acc[a0 + 0].x, acc[a0 + 0].y), pack_bf16x2(acc[a0 + 1].x, acc[a0 + 1].y),
-                                             pack_bf16x2(acc[a0 + 2].x, acc[a0 + 2].y), pack_bf16x2(acc[a0 + 3].x, acc[a0 + 3].y));
-                            }
-                            __syncwarp();
-                            __nv_bfloat16* dst = p.c + (size_t)slab_row0 * p.n + (col0 + ch * 64 + 8 * c8);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int r = 4 * i + rsub;
-                                const uint4 q = ld_shared_v4(slab0 + r * 128 + ((c8 ^ (r & 7)) << 4));
-                                if (slab_row0 + r < p.m) *reinterpret_cast<uint4*>(dst + (size_t)r * p.n) = q;
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int ch = 0; ch < CPT / 32; ++ch) {
-                            if (col0 + ch * 32 >= p.n) break;
-                            __syncwarp();
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int a0 = ch * 16 + j * 2;
-                                st_shared_v4(my_row + ((j ^ (lane & 7)) << 4), __float_as_uint(acc[a0].x),
-                                             __float_as_uint(acc[a0].y), __float_as_uint(acc[a0 + 1].x),
-                                             __float_as_uint(acc[a0 + 1].y));
-                            }
-                            __syncwarp();
-                            float* dst = p.partial + ((size_t)t.split * p.m + slab_row0) * p.n + (col0 + ch * 32 + 4 * c8);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int r = 4 * i + rsub;
-                                const uint4 q = ld_shared_v4(slab0 + r * 128 + ((c8 ^ (r & 7)) << 4));
-                                if (slab_row0 + r < p.m) *reinterpret_cast<uint4*>(dst + (size_t)r * p.n) = q;
-                            }
-                        }
-                    }
-                } else
-                // TMA form (several destinations, or direct_store off): one lane hands the slab to the TMA, which
-                // clips rows >= m / columns >= n.  Consecutive stores of this warp alternate over its kSlabs slabs
-                // (n_stores counts them across tiles, so skipped chunks of a ragged tile cannot break the
-                // alternation); before a slab is rewritten, the store that last read it (kSlabs commit groups
-                // ago) must have finished reading.
+                // One lane hands the slab to the TMA, which clips rows >= m / columns >= n.  Consecutive stores of
+                // this warp alternate over its kSlabs slabs (n_stores counts them across tiles, so skipped chunks
+                // of a ragged tile cannot break the alternation); before a slab is rewritten, the store that last
+                // read it (kSlabs commit groups ago) must have finished reading.  (Reading the slab back and
+                // writing C with ordinary vector stores was measured: 20 % slower on the short-K shapes.)
                 if (p.splits == 1) {
 #pragma unroll
                     for (int ch = 0; ch < CPT / 64; ++ch) {

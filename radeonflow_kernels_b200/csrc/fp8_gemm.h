@@ -24,7 +24,6 @@ struct GemmParams {
     const int* fnuz_flags;  // nullptr, or two device words left by the e4m3fnuz conversion pass (reference-layout
                             // entry only): [0] / [1] != 0 = read A / B from the converted copy (dests.m[0] / m[1])
     int dest_first;         // first destination to store to (N-split: own rank, so ranks target different GPUs)
-    int direct_store;       // 1: one-destination tiles leave through vector stores (default); 0: through TMA stores
 };
 
 // Output tensor maps of an N-split GEMM: entry d addresses GPU d's full row-major C.

@@ -137,7 +137,6 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
     p.c_col_offset = 0;
     p.dest_first = 0;
     p.fnuz_flags = nullptr;
-    p.direct_store = 1;
     cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, nullptr, p, bn, sd->num_sms,
                                         reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {

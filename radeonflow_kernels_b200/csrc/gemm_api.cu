@@ -38,17 +38,6 @@ bool pair_config_enabled() {
     return v == 1;
 }
 
-// RF_FP8_GEMM_DIRECT_STORE=0 sends one-destination tiles through TMA stores instead of vector stores
-// (measurement knob; the N-split GEMM always uses TMA stores for its peer copies).
-bool direct_store_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("RF_FP8_GEMM_DIRECT_STORE");
-        v = (e && e[0] == '0') ? 0 : 1;
-    }
-    return v == 1;
-}
-
 struct GemmPlan {
     int block_n;
     int splits;
@@ -194,7 +183,6 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     p.n_dest = n_dest;
     p.c_col_offset = col_offset;
     p.fnuz_flags = nullptr;
-    p.direct_store = direct_store_enabled() ? 1 : 0;
     p.dest_first = (n_dest > 1 && dest_n > 0 && n > 0) ? (col_offset / n) % n_dest : 0;   // = rank for an N-split
     rf::GemmDestMaps dests;
     bool use_dests = false;

@@ -16,7 +16,7 @@ constexpr int kMaxDevices = 64;
 struct DeviceState {
     bool init = false;
     int num_sms = 0;
-    int* status = nullptr;          // device status area: kStatusWords 32-bit words (layout in ptx.cuh)
+    int* status = nullptr;          // device status area: kStatusWords 32-bit words (layout in status_words.h)
     void* scratch[4] = {nullptr, nullptr, nullptr, nullptr};   // library-owned growable buffers, see ScratchSlot
     size_t scratch_bytes[4] = {0, 0, 0, 0};
 };

@@ -67,8 +67,8 @@ def fp8_mm_reference_layout(a, b, a_scale, b_scale, c, fnuz=None):
     No transposed copy is made: the library reads the operands in place as MN-major tiles.
 
     ``fnuz``: whether the bytes are e4m3fnuz (the reference's dtype); None = decide from the dtype, with
-    uint8 read as e4m3fn.  An e4m3fnuz operand must not hold NaN (0x80) or +-240 (0x7F / 0xFF);
-    `device_status()` reports 16 after a call that met one.
+    uint8 read as e4m3fn.  An e4m3fnuz operand that holds +-240 (0x7F / 0xFF, as amax-scaled data does) or
+    NaN (0x80) is computed from a converted copy; `device_status()` then reports the note 16 once.
     """
     if not all(t.is_cuda for t in (a, b, a_scale, b_scale, c)):
         raise ValueError("fp8_mm_reference_layout: all tensors must be CUDA tensors (there is no CPU path)")
@@ -111,7 +111,9 @@ def custom_kernel(data):
 
 
 def device_status() -> int:
-    """Synchronises and returns the raw device status word (0 = no bounded wait expired)."""
+    """Synchronises, returns and clears the device status: the code (1-6) of a bounded device-side wait that
+    expired, else a note that stopped nothing (16: e4m3fnuz operand read from converted bytes; 32:
+    expert-parallel receive buffer overflow), else 0."""
     detail = ctypes.c_int(0)
     _lib.lib().rf_device_status(ctypes.byref(detail))
     return detail.value

@@ -185,6 +185,35 @@ def test_perf_metrics_are_filled(rf_lib):
     assert pm.count >= 1 and pm.entries[0].time > 0 and pm.entries[0].gflops > 0
 
 
+@pytest.mark.parametrize("m,n,k,split", [(1024, 1536, 7168, 3), (1024, 576, 7168, 3), (1024, 512, 7168, 4),
+                                         (300, 320, 2048, 8), (130, 64, 1024, 2), (6144, 512, 7168, 2)])
+def test_library_scratch_and_caller_scratch_give_the_same_bits(rf_lib, m, n, k, split):
+    """`run` (library-owned split-K scratch, plan from the table) against `rf_fp8_gemm` (caller's scratch, explicit
+    split): same kernels, same slice order in the fix-up (src/gemm/gemm_kernel.cpp:288-303), so the same bits;
+    twice in a row, because the library's scratch is reused."""
+    a, b, a_s, b_s = o.generate_input(m, n, k, 77 + split, "randn")
+    da, db, das, dbs = gemm_device_inputs(a, b, a_s, b_s)
+    ws = torch.empty(split * m * n * 4, dtype=torch.uint8, device="cuda:0")
+    full2, c2 = canary_output(m, n)
+    assert rf_lib.rf_fp8_gemm(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(), c2.data_ptr(), m, n, k,
+                              split, ws.data_ptr(), ws.numel(), None) == 0
+    assert rf_lib.rf_fp8_gemm_set_plan(m, n, k, 256 if n >= 256 else 128, split) == 0
+    try:
+        for _ in range(2):
+            full1, c1 = canary_output(m, n)
+            rf_lib.run(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(), c1.data_ptr(), m, n, k, None, None)
+            torch.cuda.synchronize()
+            assert canary_intact(full1, m, n) and canary_intact(full2, m, n)
+            assert torch.equal(c1.view(torch.uint16), c2.view(torch.uint16))
+    finally:
+        rf_lib.rf_fp8_gemm_set_plan(m, n, k, 0, 0)
+        rf_lib.rf_fp8_gemm_set_plan(1024, 1536, 7168, 256, 3)      # the built-in entries this test overwrote
+        rf_lib.rf_fp8_gemm_set_plan(1024, 576, 7168, 128, 3)
+        rf_lib.rf_fp8_gemm_set_plan(1024, 512, 7168, 128, 4)
+    assert G.device_status() == 0
+    assert_close(c1.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a, b, a_s, b_s))
+
+
 @pytest.mark.parametrize("block_n", ["512", "384"])
 def test_cta_pair_configuration_matches_oracle(block_n):
     """The cta_group::2 configurations (256 x 256 and 256 x 128 tiles per 2-CTA cluster) are selected per

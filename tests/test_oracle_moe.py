@@ -14,20 +14,35 @@ def load(path):
     z = np.load(path)
     d, f, e, ns, k, t, seed = [int(v) for v in z["cfg"]]
     w = {n[2:]: z[n] for n in z.files if n.startswith("w:")}
+    if "experts.0.0.weight" not in w:
+        # large-expert-count fixtures store the router only; the other weights come back, bit for bit, from the seed
+        x2, w2, _ = o.generate_input(d, f, e, ns, k, t, seed)
+        assert np.array_equal(x2, z["x"]) and np.array_equal(w2["router.weight"], w["router.weight"])
+        w = w2
     return z, w, dict(d=d, f=f, e=e, ns=ns, k=k, t=t, seed=seed)
 
 
 def test_golden_files_present():
-    assert len(GOLDEN) >= 3
+    assert len(GOLDEN) >= 4 and any("_e256_k8_" in p for p in GOLDEN)
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
 def test_oracle_matches_reference_output(path):
     z, w, c = load(path)
     st = o.moe_stages(z["x"][0], w, c["e"], c["k"])
-    ok, nbad, mx = o.check(st["final_output"], z["ref_out"][0], rtol=1e-2, atol=1e-2)   # the reference's tolerance
+    # A token whose k-th and (k+1)-th fp16 probabilities are equal may be routed to either expert: torch.topk,
+    # which the reference's gate uses, has no tie contract, the kernel rule is lowest index.  Such tokens (1 of
+    # 160 in the 256-expert fixture, none in the others) are compared only where both chose the same experts.
+    same = (np.sort(st["seq_experts_index"], axis=1) == np.sort(z["ref_topk_idx"], axis=1)).all(axis=1)
+    probs = o.softmax_fp16(st["expert_scores"] if "expert_scores" in st else
+                           o.router_logits(z["x"][0], w["router.weight"])).astype(np.float32)
+    srt = -np.sort(-probs, axis=1)
+    tie = (srt[:, c["k"] - 1] == srt[:, c["k"]]) if c["k"] < c["e"] else np.zeros(len(srt), bool)
+    assert np.all(same | tie) and tie.sum() <= 2
+    got, ref = st["final_output"][same], z["ref_out"][0][same]
+    ok, nbad, mx = o.check(got, ref, rtol=1e-2, atol=1e-2)   # the reference's tolerance
     assert ok, (nbad, mx)
-    ok, nbad, mx = o.check(st["final_output"], z["ref_out"][0], rtol=4e-3, atol=4e-3)   # and well inside it
+    ok, nbad, mx = o.check(got, ref, rtol=4e-3, atol=4e-3)   # and well inside it
     assert ok, (nbad, mx)
 
 
