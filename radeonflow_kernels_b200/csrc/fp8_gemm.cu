@@ -480,13 +480,18 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 for (int c = 0; c < NCH; ++c) {
                     tmem_ld_fence(v[c % NV]);   // waits for every load issued so far
                     if (NV == 2 && c + 1 < NCH) tmem_ld32_async(taddr + (c + 1) * 32, v[(c + 1) % NV]);
+#ifndef RF_LATE_RELEASE
                     if (c + 1 == NCH) { release_buffer(); RF_STAT_END(w_rel); }
+#endif
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         acc[c * 16 + j] =
                             __ffma2_rn(make_float2(v[c % NV][2 * j], v[c % NV][2 * j + 1]), s2, acc[c * 16 + j]);
                     if (NV == 1 && c + 1 < NCH) tmem_ld32_async(taddr + (c + 1) * 32, v[0]);
                 }
+#ifdef RF_LATE_RELEASE
+                release_buffer(); RF_STAT_END(w_rel);
+#endif
 #endif
             }
             if (!ok) break;

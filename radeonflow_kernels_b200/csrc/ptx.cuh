@@ -94,13 +94,18 @@ __device__ __forceinline__ unsigned long long wait_limit_ns(const int* status) {
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code, int tag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    // The polling loop stays as small as possible (the waiting warps share their schedulers with the warps
+    // that do the work); the clock is first read after 256 failed polls, so a wait that ends within a few
+    // microseconds never touches it.
+    unsigned long long t0 = 0;
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 0xffu) == 0) {
             const int seen = *reinterpret_cast<volatile int*>(status);
             if (seen != 0 && (seen >> kStatusTagShift) == tag) return false;
-            if (globaltimer_ns() - t0 > wait_limit_ns(status)) {
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > wait_limit_ns(status)) {
                 atomicCAS(status, 0, code | (tag << kStatusTagShift));
                 return false;
             }
