@@ -323,6 +323,17 @@ int rf_moe_grouped_gemm(const void *x, int n_rows, const void *const *w_ptrs_hos
  * (hipBLASLt takes raw pointers, src/moe/gemm_thirdparty.cpp:65-115).                               */
 int rf_moe_set_map_cache_sets(int max_sets);
 
+/* on != 0: rf_moe_forward and rf_run_from_python let the first expert GEMM gather the token rows in its
+ * own loader (expand_input, src/moe/moe_topk_kernel.cpp:174-213, fused) and leave expanded_seq_input
+ * unwritten; run_topk always writes it, as the reference's checker expects.  Same bits either way.  Off by
+ * default (RF_MOE_FUSED_GATHER=1 turns it on at first use): measured, the separate gather pass is faster.  */
+int rf_moe_set_fused_gather(int on);
+
+/* Grid cap of the grouped GEMMs that THIS host thread enqueues from now on (0 = one persistent CTA per SM,
+ * the default).  The expert-parallel layer uses it to leave SMs to its dispatch kernel while the shared
+ * expert runs.  No reference counterpart.                                                             */
+int rf_moe_set_grid_limit(int max_ctas);
+
 /* Router logits expert_scores[t, e] = fp16(x[t,:] . router_weight[e,:] + router_bias[e]); the
  * matmul the reference leaves to PyTorch (scripts/gen_submission.py:400).  router_bias may be NULL. */
 int rf_moe_router_gemm(const void *x, const void *router_weight, const float *router_bias, int n_tokens,
@@ -444,7 +455,9 @@ int rf_moe_ep_set_weights(RfMoeEp *ep, const void *router_weight, const float *r
 /* x: fp16 [n_tokens, d_hidden] local tokens -> out fp16 [n_tokens, d_hidden]; asynchronous on `stream`. */
 int rf_moe_ep_forward(RfMoeEp *ep, const void *x, void *out, rf_stream_t stream);
 enum { RF_MOE_EP_OPT_TRACE = 1,            /* value != 0: record an event after every stage of forward   */
-       RF_MOE_EP_OPT_DISPATCH_BLOCKS = 2   /* value > 0: grid cap of the dispatch kernel                 */ };
+       RF_MOE_EP_OPT_DISPATCH_BLOCKS = 2   /* value = R in 1..64: the dispatch runs as R blocks that each own
+                                              an SM and the shared expert's GEMMs on the other SMs beside it
+                                              (0, the default: dispatch blocks on every SM, the two in turn)  */ };
 int rf_moe_ep_set_option(RfMoeEp *ep, int option, int value);
 /* Milliseconds of the stages of the last traced forward (synchronises); returns the number of stages.  */
 int rf_moe_ep_stage_times(RfMoeEp *ep, float *ms, const char **names, int max_stages);

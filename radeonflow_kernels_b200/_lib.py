@@ -136,6 +136,10 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_moe_grouped_gemm.argtypes = [vp, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), vp, ci, ci, ci, vp, vp]
     L.rf_moe_router_gemm.restype = ci
     L.rf_moe_router_gemm.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp]
+    L.rf_moe_set_fused_gather.restype = ci
+    L.rf_moe_set_fused_gather.argtypes = [ci]
+    L.rf_moe_set_grid_limit.restype = ci
+    L.rf_moe_set_grid_limit.argtypes = [ci]
     L.rf_moe_set_map_cache_sets.restype = ci
     L.rf_moe_set_map_cache_sets.argtypes = [ci]
     L.rf_moe_combine.restype = ci

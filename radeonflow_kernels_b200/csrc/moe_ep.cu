@@ -55,9 +55,11 @@ ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_
 }
 
 // One row per block iteration: the row's indices are read once (not once per 16 bytes), then the
-// 256 threads move the row with up to four independent 16-byte loads in flight each before the
-// matching peer stores.
-__global__ void __launch_bounds__(256)
+// block's threads move the row with up to four independent 16-byte loads in flight each before the
+// matching peer stores.  Launched either as many 256-thread blocks spread over every SM, or (SM partition) as
+// a few 1024-thread blocks that each claim a whole SM through their shared-memory request, so that a
+// persistent GEMM with a correspondingly smaller grid runs beside them on the remaining SMs.
+__global__ void __launch_bounds__(1024)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted_experts,
                    const int* __restrict__ permuted_rows, const int* __restrict__ first_token_offset,
                    const int* __restrict__ send_base, int n_tokens, int n_pairs, int vec_per_row,
@@ -68,7 +70,10 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted
     // destination (rank+1, rank+2, ...), so at any moment the senders target different GPUs instead of
     // all writing into the same one.
     const int p0 = __ldg(first_token_offset + ((rank + 1) % world) * experts_per_rank);
-    for (int i = blockIdx.x; i < n_pairs; i += gridDim.x) {
+    // a group of 256 threads moves one row at a time: one group per block, or four in a 1024-thread block
+    const int groups_per_block = blockDim.x >> 8;
+    const int tid = threadIdx.x & 255;
+    for (int i = blockIdx.x * groups_per_block + (threadIdx.x >> 8); i < n_pairs; i += gridDim.x * groups_per_block) {
         int p = i + p0;
         if (p >= n_pairs) p -= n_pairs;
         const int e = __ldg(permuted_experts + p);
@@ -79,9 +84,9 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted
             // written past the allocation on another GPU; -1 marks the pair for the pulling combine, and
             // where results are pushed home the pair's result row is zeroed here instead
             if (drop_fill != nullptr)
-                for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += 256)
+                for (int v0 = tid; v0 < vec_per_row; v0 += 256)
                     drop_fill[(size_t)p * vec_per_row + v0] = make_uint4(0u, 0u, 0u, 0u);
-            if (threadIdx.x == 0) {
+            if (tid == 0) {
                 pair_rank[p] = -1;
                 pair_row[p] = 0;
                 atomicOr(status + kStatusDiagWord, (int)kDiagEpOverflow);
@@ -91,7 +96,7 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted
         const int tok = __ldg(permuted_rows + p) % n_tokens;
         const uint4* src = x + (size_t)tok * vec_per_row;
         uint4* dst = static_cast<uint4*>(pick_peer(recv_x, q)) + (size_t)row * vec_per_row;
-        for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += 4 * 256) {
+        for (int v0 = tid; v0 < vec_per_row; v0 += 4 * 256) {
             uint4 r[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -100,7 +105,7 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted
             for (int j = 0; j < 4; ++j)
                 if (v0 + j * 256 < vec_per_row) dst[v0 + j * 256] = r[j];
         }
-        if (threadIdx.x == 0) {
+        if (tid == 0) {
             pair_rank[p] = q;
             pair_row[p] = row;
             if (with_meta) static_cast<int*>(pick_peer(recv_meta, q))[row] = (rank << kEpMetaSlotBits) | p;
@@ -249,7 +254,28 @@ cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, c
                                    void* drop_fill, int* status, int num_sms, int max_blocks, cudaStream_t stream) {
     const int vec = row_bytes / 16;
     if (n_pairs == 0) return cudaSuccess;
-    int blocks = max_blocks > 0 ? max_blocks : num_sms * 8;
+    if (max_blocks > 0) {
+        // SM partition: `max_blocks` blocks of 1024 threads, each asking for most of an SM's shared memory so that
+        // no second block (and no CTA of the GEMM running beside it) shares its SM.  A block is four groups of 256
+        // threads, each moving a row at a time: four rows' worth of loads (64 KB) are in flight per SM.
+        constexpr int kOwnSmBytes = 160 * 1024;
+        static bool attr_set[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 64 && !attr_set[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(ep_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 kOwnSmBytes);
+            if (e != cudaSuccess) return e;
+            attr_set[dev] = true;
+        }
+        int blocks = max_blocks * 4 < n_pairs ? max_blocks : (n_pairs + 3) / 4;
+        ep_dispatch_kernel<<<(unsigned)blocks, 1024, kOwnSmBytes, stream>>>(
+            static_cast<const uint4*>(x), permuted_experts, permuted_rows, first_token_offset, send_base, n_tokens,
+            n_pairs, vec, experts_per_rank, rank, world, capacity, recv_x, recv_meta ? *recv_meta : recv_x,
+            recv_meta ? 1 : 0, pair_rank, pair_row, static_cast<uint4*>(drop_fill), status);
+        return cudaGetLastError();
+    }
+    int blocks = num_sms * 8;
     if (blocks > n_pairs) blocks = n_pairs;
     ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(x), permuted_experts,
                                                              permuted_rows, first_token_offset, send_base, n_tokens,

@@ -258,7 +258,10 @@ int rf_moe_ep_set_option(RfMoeEp* ep, int option, int value) {
     if (!ep) return RF_ERR_NULL_POINTER;
     switch (option) {
         case RF_MOE_EP_OPT_TRACE: ep->trace = value != 0; ep->n_marks = 0; return RF_OK;
-        case RF_MOE_EP_OPT_DISPATCH_BLOCKS: ep->dispatch_blocks = value > 0 ? value : 0; return RF_OK;
+        case RF_MOE_EP_OPT_DISPATCH_BLOCKS:
+            if (value < 0 || value > 64) return RF_ERR_BAD_SHAPE;
+            ep->dispatch_blocks = value;
+            return RF_OK;
         default: return RF_ERR_UNSUPPORTED;
     }
 }
@@ -301,12 +304,16 @@ int rf_moe_ep_forward(RfMoeEp* ep, const void* x, void* out, rf_stream_t stream)
                                    st->num_sms, ep->dispatch_blocks, ep->side) != cudaSuccess)
         return RF_ERR_CUDA;
     if (cudaEventRecord(ep->ev_sent, ep->side) != cudaSuccess) return RF_ERR_CUDA;
+    // SM partition: while the dispatch blocks own `dispatch_blocks` SMs, the shared expert's persistent GEMMs
+    // run with that many CTAs fewer, so both really run at the same time.
+    if (ep->dispatch_blocks > 0) rf_moe_set_grid_limit(st->num_sms - ep->dispatch_blocks);
     const void* sg[1] = {ep->s_gate};
     const void* su[1] = {ep->s_up};
     const void* sd[1] = {ep->s_down};
-    if ((rc = rf_moe_grouped_gemm(x, T, sg, su, ep->single_offsets, 1, ep->fs, d, ep->sh1, stream)) != RF_OK) return rc;
-    if ((rc = rf_moe_grouped_gemm(ep->sh1, T, sd, nullptr, ep->single_offsets, 1, d, ep->fs, ep->sh2, stream)) != RF_OK)
-        return rc;
+    rc = rf_moe_grouped_gemm(x, T, sg, su, ep->single_offsets, 1, ep->fs, d, ep->sh1, stream);
+    if (rc == RF_OK) rc = rf_moe_grouped_gemm(ep->sh1, T, sd, nullptr, ep->single_offsets, 1, d, ep->fs, ep->sh2, stream);
+    rf_moe_set_grid_limit(0);
+    if (rc != RF_OK) return rc;
     if (cudaStreamWaitEvent(s, ep->ev_sent, 0) != cudaSuccess) return RF_ERR_CUDA;
     mark(ep, s);
     if ((rc = rendezvous(ep, nullptr, s)) != RF_OK) return rc;          // every rank's dispatch has landed

@@ -10,6 +10,8 @@
 //   warp 0     TMA producer: A tile [128 x 64] fp16 (K-major, 128-byte swizzle) and B as four
 //              [64 K-rows x 64 N] boxes of the row-major weight (MN-major operand, 128-byte swizzle);
 //              in SwiGLU mode two boxes come from W_gate and two from W_up at the same columns
+//              (SwiGLU mode with a row map: warps 2 and 3 gather the A rows from the token matrix with 16-byte
+//              cp.async copies into the same swizzled layout, and the TMA loads only B)
 //   warp 1     MMA issuer: 4 x tcgen05.mma.kind::f16 (128 x 256 x 16) per stage, accumulating the
 //              whole K range in one of two 256-column TMEM buffers; one commit per stage frees the
 //              shared-memory stage, one per tile publishes the accumulator
@@ -37,6 +39,8 @@ constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 32 * (NUM_NON_EPI_WARPS + EPI_WARPS);
 constexpr int SLAB_BYTES = 32 * 128;
 constexpr int NBUF = 2;
+constexpr int GATHER_THREADS = 64;   // warps 2 and 3
+constexpr int GATHER_LAG = 2;        // cp.async groups a gather thread keeps in flight
 constexpr int TMEM_COLS = NBUF * BN;
 constexpr int BAR_BYTES = (2 * STAGES + 2 * NBUF) * 8 + 16;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * SLAB_BYTES + BAR_BYTES + 1024;
@@ -82,11 +86,13 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // gathered A rows: the stage is full when the TMA's B bytes have landed AND every gather thread has arrived
+    const bool gather = SWIGLU && p.gather_map != nullptr;
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tma_a);
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
+            mbar_init(full_bar(s), gather ? 1 + GATHER_THREADS : 1);
             mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < NBUF; ++b) {
@@ -127,10 +133,10 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1, p.status, kErrProducerWait, p.launch_tag));
                 if (!ok) break;
                 if (elect_one()) {
-                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    mbar_expect_tx(full_bar(s), gather ? B_BYTES : STAGE_BYTES);
                     const uint32_t sa = smem_base + s * STAGE_BYTES;
                     const uint32_t sb = sa + A_BYTES;
-                    tma_load_2d(sa, &tma_a, full_bar(s), ks * BK, row0);
+                    if (!gather) tma_load_2d(sa, &tma_a, full_bar(s), ks * BK, row0);
                     if (ROUTER) {
                         // B [N, K] row-major: one box of 256 rows (N) x 64 K
                         tma_load_2d(sb, mb, full_bar(s), ks * BK, n0);
@@ -182,7 +188,55 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 __syncwarp();
             }
         }
-    } else if (warp >= NUM_NON_EPI_WARPS) {
+    } else if (warp < NUM_NON_EPI_WARPS) {
+        // ------------------------------------------------- A-row gather (warps 2, 3)
+        // 8 lanes per 128-byte row segment, so every copy instruction of a warp reads four whole 128-byte
+        // segments of four token rows and writes four whole rows of the swizzled tile.  A thread keeps
+        // GATHER_LAG groups in flight; when a group has landed it makes the bytes visible to the tensor core's
+        // proxy and arrives on the stage's barrier.
+        if (gather) {
+            const int tg = threadIdx.x - 64;            // 0..63
+            const int c8 = tg & 7, rsub = tg >> 3;      // 16-byte piece of the segment; row within a group of 8
+            const __half* xsrc = static_cast<const __half*>(p.gather_src);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+                int tile, nb_i;
+                decode_item(w, p.tile_chunk, nbn, &tile, &nb_i);
+                const int row0 = __ldg(p.tile_row0 + tile);
+                int tok[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int r = min(row0 + i * 8 + rsub, p.gather_rows - 1);
+                    tok[i] = __ldg(p.gather_map + r) % p.gather_mod;
+                }
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1, p.status, kErrProducerWait, p.launch_tag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + s * STAGE_BYTES;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int r = i * 8 + rsub;     // r & 7 == rsub
+                        cp_async_16(sa + r * 128 + ((c8 ^ rsub) << 4),
+                                    xsrc + (size_t)tok[i] * p.k + ks * BK + c8 * 8);
+                    }
+                    cp_async_commit();
+                    ++it;
+                    if (it > GATHER_LAG) {
+                        cp_async_wait<GATHER_LAG>();
+                        fence_proxy_async_smem();
+                        mbar_arrive(full_bar((it - 1 - GATHER_LAG) % STAGES));
+                    }
+                }
+            }
+            // drain: the last groups, oldest first (also after a wait gave up: no copy may outlive the CTA)
+            cp_async_wait<1>();
+            if (ok && it >= 2) { fence_proxy_async_smem(); mbar_arrive(full_bar((it - 2) % STAGES)); }
+            cp_async_wait<0>();
+            if (ok && it >= 1) { fence_proxy_async_smem(); mbar_arrive(full_bar((it - 1) % STAGES)); }
+        }
+    } else {
         // ---------------------------------------------------------- epilogue
         const int ew = warp - NUM_NON_EPI_WARPS;
         const int quad = warp & 3;

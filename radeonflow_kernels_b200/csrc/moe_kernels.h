@@ -99,6 +99,13 @@ struct MoeGemmParams {
     // the expert outputs travel back to the GPUs that own the tokens from the GEMM's own epilogue).
     const int* scatter_meta;
     PeerPtrs scatter_dst;
+    // SwiGLU mode only, optional: row r of the A operand is row (gather_map[min(r, gather_rows - 1)] % gather_mod)
+    // of the fp16 [gather_mod, k] matrix gather_src (the token rows, read in place: the row gather of
+    // expand_input, src/moe/moe_topk_kernel.cpp:174-213, done by the GEMM's own loader); tma_a is then unused.
+    const void* gather_src;
+    const int* gather_map;
+    int gather_mod;
+    int gather_rows;
     int n_out;                  // output columns
     int k;                      // reduction length (multiple of 64)
     int tma_store;              // 1: full 32-row slabs leave through the output tensor map

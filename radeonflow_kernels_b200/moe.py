@@ -84,11 +84,14 @@ class MoEBuffers:
         self.raw = raw
 
 
-def moe_forward(x, weights, config, expert_scores=None, router_bias=None, metrics=None):
-    """Runs the layer; returns (output [same shape as x], MoEBuffers with every stage tensor).
+def moe_forward(x, weights, config, expert_scores=None, router_bias=None, metrics=None, fill_stages=True):
+    """Runs the layer; returns (output [same shape as x], MoEBuffers with the stage tensors).
 
-    `expert_scores` given  -> `run_topk` (the reference entry: logits are an input);
-    `expert_scores` None   -> `rf_moe_forward` (router GEMM on the device, optional fp32 bias).
+    `expert_scores` given  -> `run_topk` (the reference entry: logits are an input; every stage tensor is written);
+    `expert_scores` None   -> the router GEMM runs on the device (optional fp32 bias).  With `fill_stages` it is
+    followed by `run_topk`, so that every stage tensor of the reference's checker is written; without, the
+    one-call entry `rf_moe_forward` runs (which, with `rf_moe_set_fused_gather(1)`, lets its first expert GEMM
+    gather the token rows itself and leaves `expanded_seq_input` unwritten).
     """
     L = _lib.lib()
     buf = MoEBuffers(x, weights, config, expert_scores)
@@ -104,8 +107,15 @@ def moe_forward(x, weights, config, expert_scores=None, router_bias=None, metric
                 raise ValueError("moe: router_bias must be a contiguous CUDA float32 tensor")
             bias_ptr = router_bias.data_ptr()
             buf._keep.append(router_bias)
-        st = L.rf_moe_forward(ctypes.byref(buf.raw), bias_ptr, stream, pm)
-        _lib.check(st, "rf_moe_forward")
+        if fill_stages:
+            st = L.rf_moe_router_gemm(x.data_ptr(), weights["router.weight"].data_ptr(), bias_ptr, buf.T, buf.E, buf.d,
+                                      buf.stages["expert_scores"].data_ptr(), stream)
+            _lib.check(st, "rf_moe_router_gemm")
+            st = L.run_topk(ctypes.byref(buf.raw), stream, pm)
+            _lib.check(st, "run_topk")
+        else:
+            st = L.rf_moe_forward(ctypes.byref(buf.raw), bias_ptr, stream, pm)
+            _lib.check(st, "rf_moe_forward")
     return buf.stages["final_output"].view(x.shape), buf
 
 

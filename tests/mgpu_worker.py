@@ -97,6 +97,14 @@ def main():
     assert np.array_equal(layer.send_base.cpu().numpy(), sb)
     assert np.array_equal(layer.recv_offsets.cpu().numpy(), ro)
     assert layer.received_rows() == int(counts_all[:, rank * e_loc:(rank + 1) * e_loc].sum())
+    # SM partition: the dispatch as a few blocks that own an SM each, the shared expert's GEMMs beside them on
+    # the remaining SMs - same result, bit for bit
+    layer.set_dispatch_blocks(8)
+    out_part = layer.forward(x_loc).clone()
+    torch.cuda.synchronize()
+    layer.set_dispatch_blocks(0)
+    assert G.device_status() == 0
+    assert torch.equal(out_part, out_pull), "SM-partitioned dispatch changed the result"
     layer.close()
 
     # ---- 3. receive buffers smaller than the traffic: rows beyond the capacity are dropped and reported,

@@ -291,6 +291,28 @@ def test_combine_without_shared_then_add_rows(rf_lib):
     assert torch.equal(out1, out3)
 
 
+@pytest.mark.parametrize("d,f,e,k,t,seed", [(512, 256, 8, 2, 300, 5), (1024, 512, 64, 8, 777, 6), (7168, 2048, 4, 4, 257, 9)])
+def test_fused_row_gather_equals_the_materialised_path(rf_lib, d, f, e, k, t, seed):
+    """`rf_moe_forward` with the fused gather switched on (first expert GEMM gathers the token rows in its loader,
+    expanded_seq_input unwritten) against router GEMM + `run_topk` (expand_input as a pass of its own):
+    identical bits in every later stage."""
+    x, w, cfg = o.generate_input(d, f, e, 1, k, t, seed)
+    tx, tw = torch.from_numpy(x).to(DEV), to_dev(w)
+    out_a, buf_a = M.moe_forward(tx, tw, cfg, fill_stages=True)
+    rf_lib.rf_moe_set_fused_gather(1)
+    try:
+        out_b, buf_b = M.moe_forward(tx, tw, cfg, fill_stages=False)
+        buf_b.stages["expanded_seq_input"].fill_(float("nan"))          # nothing may depend on it
+        out_b, buf_b = M.moe_forward(tx, tw, cfg, fill_stages=False)
+    finally:
+        rf_lib.rf_moe_set_fused_gather(0)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    for name in ("expert_scores", "permuted_rows", "expanded_fc1_output", "expanded_fc2_output", "final_output"):
+        assert torch.equal(buf_a.stages[name], buf_b.stages[name]), name
+    assert torch.equal(out_a, out_b)
+
+
 @pytest.mark.gpu
 def test_grouped_gemm_scatter_equals_plain_grouped_gemm_then_permute(rf_lib):
     """`rf_moe_grouped_gemm_scatter` (the expert-parallel second GEMM, whose epilogue stores row i to row
