@@ -22,14 +22,16 @@ from . import _lib
 
 
 # --------------------------------------------------------------------------- host-side planner --
-def ep_layout_reference(counts_all: np.ndarray, rank: int):
+def ep_layout_reference(counts_all: np.ndarray, rank: int, capacity=None):
     """numpy statement of what ``rf_moe_ep_layout`` computes on the device.
 
     counts_all [world, E]: row s = number of (token, expert) pairs per global expert on source rank s.
     Expert e is owned by rank q = e // (E // world).  In the owner's receive buffer rows are ordered by
     (expert, source rank in the rotated order q, q+1, ..., q+world-1 mod world, source-local order): every
     owner walks its experts' rows starting with its own tokens, so at any moment the owners return results
-    to different GPUs.  Returns (send_base [E], recv_offsets [E/world + 1]).
+    to different GPUs.  Returns (send_base [E], recv_offsets [E/world + 1]).  With ``capacity`` (rows of the
+    receive buffers) the row ranges are clipped to it, as the device kernel does: a pair whose destination row
+    ``send_base[e] + i`` is >= capacity is not sent.
     """
     counts_all = np.asarray(counts_all, dtype=np.int64)
     world, n_experts = counts_all.shape
@@ -42,6 +44,8 @@ def ep_layout_reference(counts_all: np.ndarray, rank: int):
         before_me = sum(int(counts_all[(q + j) % world, e]) for j in range((rank - q) % world))
         send_base[e] = tot[first:e].sum() + before_me
     recv = np.concatenate([[0], np.cumsum(tot[rank * per:(rank + 1) * per])])
+    if capacity is not None:
+        recv = np.minimum(recv, int(capacity))
     return send_base.astype(np.int32), recv.astype(np.int32)
 
 

@@ -313,6 +313,29 @@ def test_fused_row_gather_equals_the_materialised_path(rf_lib, d, f, e, k, t, se
     assert torch.equal(out_a, out_b)
 
 
+def test_weight_map_cache_eviction_keeps_results_right(rf_lib):
+    """With the descriptor cache shrunk to 4 sets (a layer uses 7), every call evicts sets, some of them while
+    earlier kernels of the same call are still queued: results must stay bit-identical, call after call,
+    and nothing may be freed under a running kernel (the evicted arrays are retired behind an event)."""
+    layers = []
+    for seed in (21, 22, 23):
+        x, w, cfg = o.generate_input(256, 128, 8, 1, 2, 200, seed)
+        tx, tw = torch.from_numpy(x).to(DEV), to_dev(w)
+        layers.append((tx, tw, cfg, M.custom_kernel((tx, tw, cfg)).clone()))     # with the roomy default cache
+    torch.cuda.synchronize()
+    assert rf_lib.rf_moe_set_map_cache_sets(3) == 1            # at least four: one GEMM pins up to two sets
+    assert rf_lib.rf_moe_set_map_cache_sets(4) == 0
+    try:
+        for _ in range(3):
+            outs = [M.custom_kernel((tx, tw, cfg)) for (tx, tw, cfg, _) in layers]
+            torch.cuda.synchronize()
+            for out, (_, _, _, ref) in zip(outs, layers):
+                assert torch.equal(out, ref)
+        assert G.device_status() == 0
+    finally:
+        assert rf_lib.rf_moe_set_map_cache_sets(2048) == 0
+
+
 @pytest.mark.gpu
 def test_grouped_gemm_scatter_equals_plain_grouped_gemm_then_permute(rf_lib):
     """`rf_moe_grouped_gemm_scatter` (the expert-parallel second GEMM, whose epilogue stores row i to row

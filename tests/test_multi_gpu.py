@@ -159,6 +159,30 @@ def test_layout_planner_small_case():
     assert ro0.tolist() == [0, 5, 7] and ro1.tolist() == [0, 5, 14]
 
 
+def test_layout_planner_clips_to_the_receive_capacity():
+    """Rows beyond the capacity are never addressed: every owner's row ranges stop at it, and the pairs a sender
+    must drop are exactly those whose destination row reaches it."""
+    from radeonflow_kernels_b200.multi_gpu import ep_layout_reference
+    rng = np.random.default_rng(5)
+    world, e = 4, 16
+    per = e // world
+    counts = rng.integers(0, 9, size=(world, e))
+    for q in range(world):
+        total = int(counts[:, q * per:(q + 1) * per].sum())
+        cap = max(1, total // 2)
+        _, ro_full = ep_layout_reference(counts, q)
+        _, ro = ep_layout_reference(counts, q, capacity=cap)
+        assert ro.tolist() == np.minimum(ro_full, cap).tolist() and ro[-1] == min(total, cap)
+        # senders: rows kept + rows dropped = rows produced, and every kept row is below the capacity
+        kept = 0
+        for s in range(world):
+            sb, _ = ep_layout_reference(counts, s, capacity=cap)
+            for ex in range(q * per, (q + 1) * per):
+                rows = sb[ex] + np.arange(counts[s, ex])
+                kept += int((rows < cap).sum())
+        assert kept == min(total, cap)
+
+
 @pytest.mark.gpu
 def test_multi_gpu_worker_all_visible_gpus():
     import torch
