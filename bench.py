@@ -45,10 +45,10 @@ NK_PAIRS = [(1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), 
             (512, 7168), (4096, 512)]
 SWEEP = [(m, n, k) for m in (1024, 6144) for (n, k) in NK_PAIRS]
 # dram__bytes_read.sum + dram__bytes_write.sum of fp8_gemm_kernel for each sweep shape, in SWEEP order, from one
-# ncu pass (two DRAM counters, --clock-control none) over a sweep of `bench.py --steps 2 --warmup 3
-# --no-cpu-baseline --no-extras`.  C mostly stays in the 126 MB L2, hence traffic < algorithmic.
-NCU_DRAM_BYTES = [18623744, 6396672, 11739904, 2159104, 16898048, 40659712, 19004416, 11280640, 2690816,
-                  56950272, 14554880, 49672704, 30538752, 60639232, 114914816, 65986304, 49144320, 5449984]
+# ncu pass (two DRAM counters, --clock-control none, caches flushed before each measured launch) over the fifth
+# sweep of `bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-extras`, taken with the kernel as it is now.
+# Reads = A + B + scales once; C mostly stays in the 126 MB L2 at kernel end, hence traffic < algorithmic.
+NCU_DRAM_BYTES = [18641920, 6395648, 11742464, 2162176, 16900608, 40662272, 19006464, 11282944, 2694400, 57062912, 14552832, 49679360, 29924608, 61005824, 115116800, 65865984, 49142272, 5400832]
 # same two counters for the largest moe_gemm_kernel launch of the single-GPU MoE layer (routed fc1)
 MOE_NCU_DRAM_BYTES = 2.91e9
 METRIC = "fp8_blockscaled_gemm_tflops"
@@ -876,7 +876,8 @@ def run_gpu_arm(args):
                          "frac_of_2x_bf16_burst": achieved / fp8_assumed,
                          "frac_of_2x_bf16_sustained": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
                          "traffic": (sum(NCU_DRAM_BYTES) / len(NCU_DRAM_BYTES) if not args.shapes else None),
-                         "traffic_note": "DRAM bytes per fp8_gemm_kernel launch, mean over the 18 shapes, ncu; "
+                         "traffic_note": "DRAM bytes per fp8_gemm_kernel launch, mean over the 18 shapes, from an ncu capture "
+                                         "of one whole sweep after the warm-up sweeps (caches flushed per launch); "
                                          f"algorithmic mean {sum(gemm_bytes(*x) for x in SWEEP) / len(SWEEP):.0f}",
                          "peak_source": ("plain FP8 GEMM of the vendor library (torch._scaled_mm, e4m3 8192^3, best of 10) "
                                          "measured in this run as a yardstick" if fp8_measured else
