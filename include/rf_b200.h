@@ -68,7 +68,14 @@ void run(void *a, void *b, void *as, void *bs, void *c, int m, int n, int k, Per
  * `workspace` may be NULL when rf_fp8_gemm_workspace_bytes() returns 0 for the
  * shape; otherwise it must hold at least that many bytes (256-byte aligned).
  * `split_k` = 0 lets the library choose; >= 1 forces that many K slices
- * (reference: compile-time SPLITK_FACTOR, src/gemm/gemm_launcher.cpp:229-247). */
+ * (reference: compile-time SPLITK_FACTOR, src/gemm/gemm_launcher.cpp:229-247);
+ * RF_SPLIT_STREAMK (-1) asks for one pass whose ragged last wave of tiles is
+ * shared out over all SMs by K blocks ("stream-K": the partial sums of a tile
+ * that two or more CTAs share meet in the scratch inside the same kernel, in a
+ * fixed order; no second launch).  It has no counterpart in the reference and
+ * serves the same purpose as its split-K: shapes whose tile count leaves SMs
+ * idle.  A shape whose tiles fill whole waves runs as a plain pass.           */
+#define RF_SPLIT_STREAMK (-1)
 int rf_fp8_gemm(const void *a, const void *b, const float *as, const float *bs, void *c, int m, int n, int k,
                 int split_k, void *workspace, size_t workspace_bytes, rf_stream_t stream);
 
@@ -77,10 +84,18 @@ int rf_fp8_gemm(const void *a, const void *b, const float *as, const float *bs, 
 size_t rf_fp8_gemm_workspace_bytes(int m, int n, int k, int split_k);
 
 /* The split-K factor the library would choose for this shape on the current
- * device (reference: dispatch table, src/gemm/gemm_launcher.cpp:229-247).    */
+ * device (reference: dispatch table, src/gemm/gemm_launcher.cpp:229-247);
+ * RF_SPLIT_STREAMK when it would run the shape as a stream-K pass.            */
 int rf_fp8_gemm_choose_split(int m, int n, int k);
 
-/* Tuned-plan table: (tile width, split-K) per exact shape, consulted before the cost model.  It replaces
+/* Introspection, no GPU needed: the work CTA `cta` of a launch on `num_sms` SMs goes through, in order, as
+ * computed on the host by the code the kernel itself runs.  Four ints per piece: tile number, K slice, first
+ * K block, end K block.  block_n 128 or 256; split_k >= 1 or RF_SPLIT_STREAMK.  Returns the number of pieces
+ * (at most max_pieces are written), 0 for a CTA beyond the grid, -1 for bad arguments.                   */
+int rf_fp8_gemm_work_pieces(int m, int n, int k, int block_n, int split_k, int num_sms, int cta, int *pieces,
+                            int max_pieces);
+
+/* Tuned-plan table: (tile width, split-K or RF_SPLIT_STREAMK) per exact shape, consulted before the cost model.  It replaces
  * the reference's compile-time dispatch table and the offline tuner that regenerates it
  * (src/gemm/gemm_launcher.cpp:229-247, tuner/gemm_tuner.py:343-385, tuner/gemm_batch.py:8-27).
  * block_n: 128 or 256 (tile 128 x block_n), 512 = CTA pair (256 x 256); block_n == 0 removes the entry.
@@ -132,7 +147,8 @@ int rf_fp8_gemm_colmajor_fnuz(const void *a, const void *b, const float *as, con
  * per call.
  *
  * Limits and rules:
- *  - An explicit split_k >= 2 needs split_k * m * n * 4 bytes to fit in RF_STATIC_SCRATCH_BYTES;
+ *  - An explicit split_k >= 2 needs split_k * m * n * 4 bytes to fit in RF_STATIC_SCRATCH_BYTES (and
+ *    RF_SPLIT_STREAMK what rf_fp8_gemm_workspace_bytes reports for it);
  *    otherwise RF_ERR_WORKSPACE is returned and a message names the sizes.  split_k = 0 lets the
  *    library choose: when its usual plan for the shape would not fit, it runs the shape unsplit
  *    (split_k = 1 never needs scratch) instead of refusing.

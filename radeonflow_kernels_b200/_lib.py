@@ -93,6 +93,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rf_fp8_gemm_choose_split.argtypes = [ci, ci, ci]
     L.rf_fp8_gemm_set_plan.restype = ci
     L.rf_fp8_gemm_set_plan.argtypes = [ci, ci, ci, ci, ci]
+    L.rf_fp8_gemm_work_pieces.restype = ci
+    L.rf_fp8_gemm_work_pieces.argtypes = [ci] * 7 + [ctypes.POINTER(ci), ci]
     L.rf_fp8_gemm_get_plan.restype = ci
     L.rf_fp8_gemm_get_plan.argtypes = [ci, ci, ci, ctypes.POINTER(ci), ctypes.POINTER(ci)]
     L.rf_fp8_gemm_load_plans.restype = ci

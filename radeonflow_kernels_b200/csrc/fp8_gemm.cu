@@ -32,7 +32,7 @@ namespace rf {
 
 #ifdef RF_WAIT_STATS
 // Debug build only: cycles each role spent inside its barrier waits, summed over CTAs.
-__device__ unsigned long long g_wait_stats[8];
+__device__ unsigned long long g_wait_stats[12];
 #define RF_STAT_BEGIN() const long long _t0 = clock64()
 #define RF_STAT_END(acc) (acc) += clock64() - _t0
 #define RF_STAT_FLUSH(idx, acc) atomicAdd(&g_wait_stats[idx], (unsigned long long)(acc))
@@ -84,8 +84,9 @@ struct GemmCfg {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemBufs = 512 / BN;                // accumulator buffers in flight
     static constexpr int kTmemCols = kTmemBufs * BN;          // all 512 TMEM columns
-    // full / empty / peer-full per stage, full / empty per accumulator buffer, the TMEM address slot (16 bytes)
-    static constexpr int kBarBytes = (3 * STAGES + 2 * kTmemBufs) * 8 + 16;
+    // full / empty / peer-full per stage, full / empty per accumulator buffer, the two stream-K barriers, the
+    // TMEM address slot (16 bytes)
+    static constexpr int kBarBytes = (3 * STAGES + 2 * kTmemBufs + 2) * 8 + 16;
     static constexpr int kSlabBytes = 32 * 128;               // one slab: 32 rows x 128 B, swizzled
     static constexpr int kSlabs = SLABS;                      // slabs per epilogue warp
     static_assert(SLABS == 1 || SLABS == 2, "one or two store slabs per warp");
@@ -111,18 +112,14 @@ struct GemmCfg {
 };
 
 struct TileCoord {
-    int m_blk, n_blk, split;
+    int m_blk, n_blk;
 };
 
-// Work item -> tile.  Consecutive work items walk down M inside a band of
-// GROUP_M row blocks before moving to the next column block, so the CTAs that
-// run concurrently share B tiles (and A bands) in L2.  K slices of one tile are
-// adjacent.
-__device__ __forceinline__ TileCoord decode_work(int w, int tiles_m, int tiles_n, int splits) {
+// Tile number -> tile.  Consecutive tiles walk down M inside a band of GROUP_M row blocks before moving to
+// the next column block, so the CTAs that run concurrently share B tiles (and A bands) in L2.
+__device__ __forceinline__ TileCoord decode_tile(int tile, int tiles_m, int tiles_n) {
     constexpr int GROUP_M = 8;
     TileCoord t;
-    t.split = w % splits;
-    int tile = w / splits;
     int band = tile / (GROUP_M * tiles_n);
     int first_m = band * GROUP_M;
     int band_rows = min(GROUP_M, tiles_m - first_m);
@@ -132,7 +129,99 @@ __device__ __forceinline__ TileCoord decode_work(int w, int tiles_m, int tiles_n
     return t;
 }
 
-template <class Cfg>
+// One stretch of work of a CTA: K blocks [kb0, kb1) of work item `item` = tile * splits + K-slice number.
+struct Piece {
+    int item, kb0, kb1;
+};
+
+// First K-block unit of CTA j's share of the stream-K region (`total` units over `n_units` CTAs).
+__host__ __device__ __forceinline__ int sk_share_begin(long long total, int j, int n_units) {
+    return (int)(total * j / n_units);
+}
+
+// Contributors of the tile whose first unit is `base` and whose owner is CTA `unit`: the CTAs j < unit whose
+// share overlaps [base, owner's first unit).  sk_first_contributor gives the lowest candidate; candidates with an
+// empty share or one that ends at or below `base` contribute nothing.
+__host__ __device__ __forceinline__ int sk_first_contributor(long long total, int unit, int n_units, int base) {
+    int j = unit - 1;
+    while (j > 0 && sk_share_begin(total, j, n_units) > base) --j;
+    return j < 0 ? 0 : j;
+}
+__host__ __device__ __forceinline__ bool sk_contributes(long long total, int j, int n_units, int base) {
+    const int hi = sk_share_begin(total, j + 1, n_units);
+    return hi > base && hi > sk_share_begin(total, j, n_units);
+}
+
+// First tile of the stream-K region.
+__host__ __device__ __forceinline__ int sk_tile0(const GemmParams& p) { return p.tiles_m * p.tiles_n - p.sk_tiles; }
+
+// The sequence of pieces a CTA works through; producer, MMA issuers and epilogue each walk their own copy.
+//
+// Plain launches: work items unit, unit + n_units, ... (a work item is a tile, or one K slice of a tile; the K
+// slices of one tile are adjacent).
+// Stream-K launches (p.sk_tiles > 0): the LAST p.sk_tiles tiles form a region whose K blocks, numbered
+// tile-major, are cut into n_units equal contiguous shares, so that no SM idles in a ragged last wave.  A CTA
+// takes its share from the TOP down (so a tile that continues in the next CTA's share is started first and
+// the tile it finishes for the previous CTA comes last) and then its plain tiles.  A share boundary inside a
+// tile makes the lower CTA a contributor (it leaves its fp32 partial sums in its scratch slot and raises its
+// flag at the very beginning of its run) and the upper CTA, which holds the tile's last K block, the owner
+// (it adds the slots of the contributors, all of LOWER block index and long finished with them, and stores
+// the tile).  Waiting only ever goes to lower block indices, which are scheduled no later than the waiter.
+template <bool STREAM_K>
+struct WorkWalker;
+
+// Plain launches.  (One register of state: the epilogue's register budget is tight and its allocation fragile.)
+template <>
+struct WorkWalker<false> {
+    int w;                     // the work item drawn last
+    __host__ __device__ __forceinline__ WorkWalker(const GemmParams&, int unit, int n_units, int) { w = unit - n_units; }
+    __host__ __device__ __forceinline__ bool next(Piece& pc, const GemmParams& p, int n_units, int kb_total) {
+        w += n_units;
+        if (w >= p.tiles_m * p.tiles_n * p.splits) return false;
+        const int split = w % p.splits;
+        pc.item = w;
+        pc.kb0 = (int)((long long)kb_total * split / p.splits);
+        pc.kb1 = (int)((long long)kb_total * (split + 1) / p.splits);
+        return true;
+    }
+};
+
+// Stream-K launches (p.splits == 1, so a work item is a tile).
+template <>
+struct WorkWalker<true> {
+    int u_lo, u_hi;            // stream-K units of this CTA not yet done: [u_lo, u_hi), taken from the top
+    int w;                     // next plain tile
+    __host__ __device__ __forceinline__ WorkWalker(const GemmParams& p, int unit, int n_units, int kb_total) {
+        const long long total = (long long)p.sk_tiles * kb_total;
+        u_lo = sk_share_begin(total, unit, n_units);
+        u_hi = sk_share_begin(total, unit + 1, n_units);
+        w = unit;
+    }
+    __host__ __device__ __forceinline__ bool next(Piece& pc, const GemmParams& p, int n_units, int kb_total) {
+        if (u_hi > u_lo) {
+            const int t = (u_hi - 1) / kb_total;
+            const int base = t * kb_total;
+            const int lo = u_lo > base ? u_lo : base;
+            pc.item = sk_tile0(p) + t;
+            pc.kb0 = lo - base;
+            pc.kb1 = u_hi - base;
+            u_hi = lo;
+            return true;
+        }
+        if (w < sk_tile0(p)) {
+            pc.item = w;
+            pc.kb0 = 0;
+            pc.kb1 = kb_total;
+            w += n_units;
+            return true;
+        }
+        return false;
+    }
+};
+
+// STREAM_K: the instantiation that stream-K launches (p.sk_tiles > 0) run; plain launches run the other one, which
+// contains none of the stream-K code.
+template <class Cfg, bool STREAM_K = false>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                 const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_p,
@@ -152,7 +241,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
     auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + NBUF + b); };
     auto peer_full_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 * NBUF + s); };   // leader only
-    const uint32_t tmem_slot = bar_base + 8u * (3 * STAGES + 2 * NBUF);
+    // stream-K: "this CTA's partial sums are stored" (8 epilogue warps -> warp 3) and "the partial sums this CTA's
+    // owner piece needs have arrived" (warp 3 -> epilogue warps); each is used at most once per launch
+    const uint32_t sk_stored_bar = bar_base + 8u * (3 * STAGES + 2 * NBUF);
+    const uint32_t sk_ready_bar = sk_stored_bar + 8u;
+    const uint32_t tmem_slot = bar_base + 8u * (3 * STAGES + 2 * NBUF + 2);
     uint32_t* tmem_slot_ptr =
         reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
@@ -180,6 +273,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             mbar_init(empty_bar(s), 1);
         }
         for (int s = 0; s < STAGES; ++s) mbar_init(peer_full_bar(s), 1);
+        if (STREAM_K) {
+            mbar_init(sk_stored_bar, Cfg::kEpiWarps);
+            mbar_init(sk_ready_bar, 1);
+        }
         for (int b = 0; b < NBUF; ++b) {
             mbar_init(tmem_full_bar(b), 1);
             // in a CTA pair the leader's barrier collects the epilogue warps of both CTAs
@@ -205,7 +302,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     // previous kernel in the stream may still be producing.
     griddep_wait();
 
-    const int total_work = p.tiles_m * p.tiles_n * p.splits;
     const int kb_total = p.k / BK;
 
     if (warp < NUM_NON_EPI_WARPS) {
@@ -228,14 +324,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             if (p.fnuz_flags[0] != 0) map_a = &dests.m[0];
             if (p.fnuz_flags[1] != 0) map_b = &dests.m[1];
         }
-        for (int w = unit; w < total_work && ok; w += unit_stride) {
-            const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
-            const int kb0 = (int)((long long)kb_total * t.split / p.splits);
-            const int kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
+        WorkWalker<STREAM_K> walk(p, unit, unit_stride, kb_total);
+        Piece pc;
+        while (ok && walk.next(pc, p, unit_stride, kb_total)) {
+            const TileCoord t = decode_tile(pc.item / p.splits, p.tiles_m, p.tiles_n);
             // rows of A and of B this CTA fetches (a CTA pair splits both between its two CTAs)
             const int a_row0 = TWO ? (t.m_blk * 2 + (int)cta_rank) * BM : t.m_blk * BM;
             const int b_row0 = t.n_blk * BN + (TWO ? (int)cta_rank * Cfg::kBRows : 0);
-            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            for (int kb = pc.kb0; kb < pc.kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 { RF_STAT_BEGIN();
@@ -277,11 +373,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         uint32_t it = 0;
         bool ok = true;
         long long w_tmem = 0, w_full = 0, w_issue = 0; (void)w_tmem; (void)w_full; (void)w_issue;
-        for (int w = unit; w < total_work && ok; w += unit_stride) {
-            const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
-            const int kb0 = (int)((long long)kb_total * t.split / p.splits);
-            const int kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
-            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        WorkWalker<STREAM_K> walk(p, unit, unit_stride, kb_total);
+        Piece pc;
+        while (ok && walk.next(pc, p, unit_stride, kb_total)) {
+            for (int kb = pc.kb0; kb < pc.kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 const int buf = it % NBUF;
@@ -337,6 +432,41 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             }
         }
         if (lane == 0) { RF_STAT_FLUSH(1, w_tmem); RF_STAT_FLUSH(2, w_full); RF_STAT_FLUSH(6, w_issue); }
+    } else if (STREAM_K && warp == 3) {
+        // ------------------------------------------------- stream-K flag keeper
+        // The fence that publishes this CTA's partial sums and the acquiring polls on other CTAs' flags cost
+        // microseconds; this otherwise idle warp pays them, so the epilogue warps only store, load and pass two
+        // shared-memory barriers.  (Memory order: epilogue stores -> mbarrier arrive [release.cta] -> this warp's
+        // wait [acquire.cta] -> fence.acq_rel.gpu -> flag store; and on the other side flag load [acquire.gpu]
+        // -> mbarrier arrive -> epilogue wait -> loads.  Both chains are causality-ordered.)
+        const unsigned long long token = p.sk_token;
+        unsigned long long* sk_flags = reinterpret_cast<unsigned long long*>(
+            reinterpret_cast<char*>(p.partial) + (size_t)unit_stride * (BM * BN * sizeof(float)));
+        const long long total = (long long)p.sk_tiles * kb_total;
+        const int u_lo = sk_share_begin(total, unit, unit_stride);
+        const int u_hi = sk_share_begin(total, unit + 1, unit_stride);
+        bool ok = true;
+        if (u_hi > u_lo && u_hi % kb_total != 0) {
+            // the top of the share stops inside a tile: the first piece leaves partial sums
+            ok = __all_sync(0xffffffffu, mbar_wait(sk_stored_bar, 0, p.status, kErrSchedWait, p.launch_tag));
+            if (ok) {
+                __threadfence();
+                if (lane == 0) st_release_gpu_u64(sk_flags + unit, token);
+            }
+        }
+        const int base = u_lo / kb_total * kb_total;       // first unit of the tile the share starts in
+        if (ok && u_lo != base && u_hi >= base + kb_total) {
+            // the bottom of the share starts inside a tile and reaches that tile's end: the last piece owns the
+            // tile.  Its contributors are the CTAs below whose shares overlap the tile.
+            for (int j = sk_first_contributor(total, unit, unit_stride, base); j < unit && ok; ++j) {
+                if (!sk_contributes(total, j, unit_stride, base)) continue;
+                ok = __all_sync(0xffffffffu, flag_wait_u64(sk_flags + j, token, p.status, kErrSchedWait, p.launch_tag));
+                // consumed: cleared for the next launch that uses this scratch (a replayed graph carries the
+                // same number every time)
+                if (ok && lane == 0) sk_flags[j] = 0ull;
+            }
+            if (ok && lane == 0) mbar_arrive(sk_ready_bar);
+        }
     }
     } else {
         // ---------------------------------------------------------- epilogue
@@ -350,6 +480,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         uint32_t n_stores = 0;        // tile-store chunks issued by this warp so far
         bool ok = true;
         long long w_acc = 0, w_total = 0, w_rel = 0; (void)w_acc; (void)w_total; (void)w_rel;
+        long long w_skw = 0, w_skf = 0, w_skr = 0; (void)w_skw; (void)w_skf; (void)w_skr;
 #ifdef RF_WAIT_STATS
         const long long t_begin = clock64();
 #endif
@@ -378,10 +509,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         int kb0 = 0, kb1 = 0;
         const float* as_row = p.a_scale;
         const float* bs_row = p.b_scale;
-        auto begin_tile = [&](int wi) {
-            const TileCoord t = decode_work(wi, p.tiles_m, p.tiles_n, p.splits);
-            kb0 = (int)((long long)kb_total * t.split / p.splits);
-            kb1 = (int)((long long)kb_total * (t.split + 1) / p.splits);
+        auto begin_piece = [&](const Piece& pc) {
+            const TileCoord t = decode_tile(pc.item / p.splits, p.tiles_m, p.tiles_n);
+            kb0 = pc.kb0;
+            kb1 = pc.kb1;
             const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
             const int row = cta_m_blk * BM + row_in_tile;
             const int col0 = t.n_blk * BN + grp * CPT;
@@ -394,11 +525,58 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 qb[d] = __ldg(bs_row + kk * bs_ks);
             }
         };
-        for (int w = unit; w < total_work && ok; w += unit_stride) {
-            begin_tile(w);
+        WorkWalker<STREAM_K> walk(p, unit, unit_stride, kb_total);
+        Piece pc;
+        while (ok && walk.next(pc, p, unit_stride, kb_total)) {
+            begin_piece(pc);
             float2 acc[CPT / 2];
+            bool fresh = true;        // the accumulators still have to be cleared
+            if (STREAM_K && kb0 > 0 && kb1 == kb_total) {
+                // Stream-K owner piece (the tile's last K blocks; always this CTA's last piece of the region):
+                // the accumulators start from the partial sums that lower CTAs left in their scratch slots at
+                // the very beginning of their runs, added in ascending K order (a fixed order for a given grid,
+                // so results do not depend on timing).  The loads are in flight while the pipeline fills.
+                { RF_STAT_BEGIN();
+                ok = __all_sync(0xffffffffu, mbar_wait(sk_ready_bar, 0, p.status, kErrSchedWait, p.launch_tag));
+                RF_STAT_END(w_skf); }
+                if (!ok) break;
+                RF_STAT_BEGIN();
+                const long long total = (long long)p.sk_tiles * kb_total;
+                const int base = (pc.item - sk_tile0(p)) * kb_total;      // the tile's first unit
+                for (int j = sk_first_contributor(total, unit, unit_stride, base); j < unit; ++j) {
+                    if (!sk_contributes(total, j, unit_stride, base)) continue;
+                    const float4* src = reinterpret_cast<const float4*>(p.partial) + (size_t)j * (BM * BN / 4) +
+                                        ((int)threadIdx.x - 32 * NUM_NON_EPI_WARPS);
+                    if (fresh) {
 #pragma unroll
-            for (int j = 0; j < CPT / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+                        for (int q = 0; q < CPT / 4; ++q) {
+                            const float4 t4 = __ldcg(src + q * (32 * Cfg::kEpiWarps));
+                            acc[2 * q] = make_float2(t4.x, t4.y);
+                            acc[2 * q + 1] = make_float2(t4.z, t4.w);
+                        }
+                        fresh = false;
+                    } else {
+#pragma unroll
+                        for (int q0 = 0; q0 < CPT / 4; q0 += 8) {
+                            float4 t4[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) t4[i] = __ldcg(src + (q0 + i) * (32 * Cfg::kEpiWarps));
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                acc[2 * (q0 + i)].x += t4[i].x;
+                                acc[2 * (q0 + i)].y += t4[i].y;
+                                acc[2 * (q0 + i) + 1].x += t4[i].z;
+                                acc[2 * (q0 + i) + 1].y += t4[i].w;
+                            }
+                        }
+                    }
+                }
+                RF_STAT_END(w_skr);
+            }
+            if (fresh) {
+#pragma unroll
+                for (int j = 0; j < CPT / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+            }
 #if RF_EPI_WIDE
             // two 32-column staging buffers, reloaded in place
             float v[2][32];
@@ -495,11 +673,27 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #endif
             }
             if (!ok) break;
+            if (STREAM_K && kb1 < kb_total) {
+                // Stream-K contributor piece (always this CTA's first piece): the 128 x BN fp32 partial sums go to
+                // this CTA's scratch slot, laid out [float4 number][epilogue thread] so that writer and reader,
+                // which map threads to elements alike, move whole 512-byte lines.  Warp 3 publishes them.
+                RF_STAT_BEGIN();
+                float4* dst = reinterpret_cast<float4*>(p.partial) + (size_t)unit * (BM * BN / 4) +
+                              ((int)threadIdx.x - 32 * NUM_NON_EPI_WARPS);
+#pragma unroll
+                for (int q = 0; q < CPT / 4; ++q)
+                    __stcg(dst + q * (32 * Cfg::kEpiWarps),
+                           make_float4(acc[2 * q].x, acc[2 * q].y, acc[2 * q + 1].x, acc[2 * q + 1].y));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sk_stored_bar);
+                RF_STAT_END(w_skw);
+                continue;
+            }
             // Tile store: each warp stages its 32 rows x 128 bytes in its own swizzled shared-memory slab, so
             // that global memory is written in whole 128-byte row segments.
             {
                 constexpr int SL = Cfg::kSlabs;
-                const TileCoord t = decode_work(w, p.tiles_m, p.tiles_n, p.splits);
+                const TileCoord t = decode_tile(pc.item / p.splits, p.tiles_m, p.tiles_n);
                 const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
                 const int col0 = t.n_blk * BN + grp * CPT;
                 const uint32_t slab0 = slab_base + ew * SL * Cfg::kSlabBytes;
@@ -563,7 +757,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_3d(&tma_p, slab, col0 + ch * 32, slab_row0, t.split);
+                            tma_store_3d(&tma_p, slab, col0 + ch * 32, slab_row0, pc.item % p.splits);
                             tma_store_commit();
                         }
                     }
@@ -582,6 +776,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             RF_STAT_FLUSH(3, w_acc);
             RF_STAT_FLUSH(4, clock64() - t_begin);
             RF_STAT_FLUSH(5, w_rel);
+            RF_STAT_FLUSH(7, w_skw);
+            RF_STAT_FLUSH(8, w_skf);
+            RF_STAT_FLUSH(9, w_skr);
         }
 #endif
     }
@@ -693,14 +890,14 @@ bool short_k_config(const GemmParams& p) {
     return on && p.splits == 1 && p.k <= 4 * BK;
 }
 
-template <class Cfg>
+template <class Cfg, bool STREAM_K = false>
 cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
                        const CUtensorMap& tma_p, const GemmDestMaps& dests, const GemmParams& p, int num_sms,
                        cudaStream_t stream) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = fp8_gemm_kernel<Cfg>;
+    auto kernel = fp8_gemm_kernel<Cfg, STREAM_K>;
     if (dev < 64 && !attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
         if (e != cudaSuccess) return e;
@@ -708,7 +905,8 @@ cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const
     }
     const int total = p.tiles_m * p.tiles_n * p.splits;
     if (!Cfg::kTwoCta) {
-        const int grid = total < num_sms ? total : num_sms;
+        // a stream-K launch shares K blocks out over exactly num_sms CTAs, whatever the tile count
+        const int grid = (total < num_sms && p.sk_tiles == 0) ? total : num_sms;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid, 1, 1);
         cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
@@ -740,12 +938,37 @@ cudaError_t launch_cfg(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const
 
 }  // namespace
 
+namespace {
+template <bool STREAM_K>
+int walk_pieces(const GemmParams& p, int unit, int n_units, int* out, int max_pieces) {
+    const int kb_total = p.k / BK;
+    WorkWalker<STREAM_K> walk(p, unit, n_units, kb_total);
+    Piece pc;
+    int n = 0;
+    while (walk.next(pc, p, n_units, kb_total)) {
+        if (n < max_pieces) {
+            out[4 * n + 0] = pc.item / p.splits;
+            out[4 * n + 1] = pc.item % p.splits;
+            out[4 * n + 2] = pc.kb0;
+            out[4 * n + 3] = pc.kb1;
+        }
+        ++n;
+    }
+    return n;
+}
+}  // namespace
+
+int fp8_gemm_walk_pieces(const GemmParams& p, int unit, int n_units, int* out, int max_pieces) {
+    return p.sk_tiles > 0 ? walk_pieces<true>(p, unit, n_units, out, max_pieces)
+                          : walk_pieces<false>(p, unit, n_units, out, max_pieces);
+}
+
 #ifdef RF_WAIT_STATS
 extern "C" void rf_debug_wait_stats(unsigned long long* out8, int reset) {
     cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out8, g_wait_stats, sizeof(unsigned long long) * 8);
+    cudaMemcpyFromSymbol(out8, g_wait_stats, sizeof(unsigned long long) * 12);
     if (reset) {
-        unsigned long long z[8] = {};
+        unsigned long long z[12] = {};
         cudaMemcpyToSymbol(g_wait_stats, z, sizeof(z));
     }
 }
@@ -764,9 +987,10 @@ cudaError_t fp8_fnuz_convert_launch(const void* src, void* dst, size_t n_bytes, 
 }
 
 namespace {
-template <class Cfg>
+template <class Cfg, bool STREAM_K = false>
 cudaError_t prepare_cfg() {
-    return cudaFuncSetAttribute(fp8_gemm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    return cudaFuncSetAttribute(fp8_gemm_kernel<Cfg, STREAM_K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Cfg::kSmemBytes);
 }
 }  // namespace
 
@@ -774,6 +998,8 @@ cudaError_t fp8_gemm_prepare_device() {
     cudaError_t e;
     if ((e = prepare_cfg<Cfg128>()) != cudaSuccess) return e;
     if ((e = prepare_cfg<Cfg256>()) != cudaSuccess) return e;
+    if ((e = prepare_cfg<Cfg128, true>()) != cudaSuccess) return e;
+    if ((e = prepare_cfg<Cfg256, true>()) != cudaSuccess) return e;
     if ((e = prepare_cfg<Cfg256ShortK>()) != cudaSuccess) return e;
     if ((e = prepare_cfg<CfgPair>()) != cudaSuccess) return e;
     if ((e = prepare_cfg<CfgPair128>()) != cudaSuccess) return e;
@@ -794,6 +1020,12 @@ cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, 
     }
     // block_n: 128 / 256 = one-CTA tiles of that width; 512 / 384 = the CTA-pair configurations (256 x 256 and
     // 256 x 128 per pair)
+    if (p.sk_tiles > 0) {
+        // stream-K: row-major operands, one destination, the one-CTA tiles
+        if (mn_major || gemm_is_pair(block_n) || p.splits != 1 || p.n_dest > 1) return cudaErrorInvalidValue;
+        return block_n == 256 ? launch_cfg<Cfg256, true>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
+                              : launch_cfg<Cfg128, true>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream);
+    }
     cudaError_t e = mn_major
                         ? (block_n == 256 ? launch_cfg<Cfg256Mn>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream)
                                           : launch_cfg<Cfg128Mn>(tma_a, tma_b, tma_c, tma_p, *dests, p, num_sms, stream))

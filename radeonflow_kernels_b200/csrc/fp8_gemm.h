@@ -21,10 +21,23 @@ struct GemmParams {
     long long as_row_stride, as_k_stride, bs_row_stride, bs_k_stride;
     int n_dest;             // copies of C to write (1, or the number of GPUs of an N-split GEMM)
     int c_col_offset;       // column of this GEMM's C inside each destination matrix
-    const int* fnuz_flags;  // nullptr, or two device words left by the e4m3fnuz conversion pass (reference-layout
-                            // entry only): [0] / [1] != 0 = read A / B from the converted copy (dests.m[0] / m[1])
+    // (Measured on B200: with 16 more bytes of kernel parameters the short kernels ran 0.3-0.4 us slower per
+    // launch, so the struct stays at 128 bytes.  The two members of the union are never used by one launch.)
+    union {
+        const int* fnuz_flags;          // nullptr, or two device words left by the e4m3fnuz conversion pass
+                                        // (reference-layout entry only): [0] / [1] != 0 = read A / B from the
+                                        // converted copy (dests.m[0] / m[1])
+        unsigned long long sk_token;    // stream-K: the value of a raised flag in this launch
+    };
     int dest_first;         // first destination to store to (N-split: own rank, so ranks target different GPUs)
+    // Stream-K (splits == 1, row-major operands, one destination): the last sk_tiles tiles are shared out by K
+    // blocks over all CTAs of the grid (which then has exactly num_sms CTAs).  `partial` holds one 128 x block_n
+    // fp32 slot per CTA, followed by one 64-bit flag per CTA; a flag is raised when it holds sk_token and is
+    // cleared by the CTA that consumes it, so stale contents never pass for a raised flag.
+    int sk_tiles;
+    GemmParams() : fnuz_flags(nullptr), sk_tiles(0) {}
 };
+static_assert(sizeof(GemmParams) == 128, "kernel parameter block of the GEMM");
 
 // Output tensor maps of an N-split GEMM: entry d addresses GPU d's full row-major C.
 struct GemmDestMaps {
@@ -39,6 +52,22 @@ inline int gemm_tile_rows(int block_n) { return gemm_is_pair(block_n) ? 256 : 12
 inline int gemm_tile_cols(int block_n) { return block_n == 512 ? 256 : (block_n == 384 ? 128 : block_n); }
 inline int gemm_b_box_rows(int block_n) { return block_n == 512 ? 128 : (block_n == 384 ? 64 : block_n); }
 
+// Scratch a stream-K launch needs: per CTA one fp32 tile slot, then one 64-bit flag per CTA.
+inline size_t gemm_streamk_slot_bytes(int block_n) { return (size_t)128 * gemm_tile_cols(block_n) * sizeof(float); }
+// Value of a raised stream-K flag: a fixed upper half and a per-launch number (never 0).
+inline unsigned long long gemm_streamk_token(unsigned epoch) { return 0x5246534B00000000ull | epoch; }
+inline size_t gemm_streamk_bytes(int block_n, int num_sms) {
+    return (size_t)num_sms * (gemm_streamk_slot_bytes(block_n) + sizeof(unsigned long long));
+}
+// Tiles of the stream-K region for `tiles` tiles on `num_sms` CTAs: the ragged last wave plus one full wave
+// (every CTA then gets between one and two tiles' worth of K blocks), or everything when there is less than
+// one wave; 0 when the tiles fill whole waves.
+inline int gemm_streamk_tiles(int tiles, int num_sms) {
+    const int rem = tiles % num_sms;
+    if (rem == 0) return 0;
+    return tiles < num_sms ? tiles : rem + num_sms;
+}
+
 // Launches the GEMM (and the split-K fix-up when p.splits > 1) on `stream`.
 // `block_n` is the configuration the tensor map of B and p.tiles_m / p.tiles_n were built for.
 // `tma_c` stores bf16 C boxes of 32 rows x 64 columns; `tma_p` (used when p.splits > 1) stores fp32
@@ -49,6 +78,12 @@ inline int gemm_b_box_rows(int block_n) { return block_n == 512 ? 128 : (block_n
 cudaError_t fp8_gemm_launch(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const CUtensorMap& tma_c,
                             const CUtensorMap& tma_p, const GemmDestMaps* dests, const GemmParams& p, int block_n,
                             int num_sms, cudaStream_t stream, bool mn_major = false);
+
+// The pieces (tile, K slice, first K block, end K block: four ints each) that CTA `unit` of `n_units` works
+// through for launch parameters `p`, in order, computed on the host by the same code the kernel runs (only
+// p.k, p.tiles_m, p.tiles_n, p.splits and p.sk_tiles are read).  Returns the number of pieces; at most
+// `max_pieces` are written.
+int fp8_gemm_walk_pieces(const GemmParams& p, int unit, int n_units, int* out, int max_pieces);
 
 // One pass over `n_bytes` (multiple of 16) of e4m3fnuz data: writes the e4m3fn bytes of equal value to `dst`
 // and sets *flag (device word, cleared first) when the operand holds a byte that cannot be consumed as it

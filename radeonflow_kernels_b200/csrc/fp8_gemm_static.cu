@@ -89,11 +89,14 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
     int rc = static_setup(&sd);
     if (rc != RF_OK) return rc;
 
+    if (split_k < -1) return RF_ERR_BAD_SHAPE;
     int bn = 128, splits = 1;
     rf::fp8_gemm_plan(m, n, k, sd->num_sms, split_k, &bn, &splits);
-    size_t need = splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
-    if (need > kStaticScratchBytes && split_k <= 0) {
-        // the library's own choice must fit the built-in array: fall back to the unsplit plan
+    const bool streamk = splits == -1;      // one pass, ragged last wave shared out by K blocks
+    size_t need = streamk ? rf::gemm_streamk_bytes(bn, sd->num_sms)
+                          : (splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0);
+    if (need > kStaticScratchBytes && split_k == 0) {
+        // the library's own choice must fit the built-in array: fall back to the plain single pass
         rf::fp8_gemm_plan(m, n, k, sd->num_sms, 1, &bn, &splits);
         need = 0;
     }
@@ -130,13 +133,17 @@ extern "C" int rf_fp8_gemm_static_scratch(const void* a, const void* b, const fl
     p.m = m; p.n = n; p.k = k;
     p.tiles_m = (m + rf::gemm_tile_rows(bn) - 1) / rf::gemm_tile_rows(bn);
     p.tiles_n = (n + rf::gemm_tile_cols(bn) - 1) / rf::gemm_tile_cols(bn);
-    p.splits = splits;
+    p.splits = splits > 1 ? splits : 1;
+    if (splits == -1) {
+        p.partial = sd->scratch;
+        p.sk_tiles = rf::gemm_streamk_tiles(p.tiles_m * p.tiles_n, sd->num_sms);
+        p.sk_token = rf::gemm_streamk_token(rf::next_streamk_epoch());
+    }
     p.as_row_stride = k / 128; p.as_k_stride = 1;
     p.bs_row_stride = k / 128; p.bs_k_stride = 1;
     p.n_dest = 1;
     p.c_col_offset = 0;
     p.dest_first = 0;
-    p.fnuz_flags = nullptr;
     cudaError_t e = rf::fp8_gemm_launch(ta, tb, tc, tp, nullptr, p, bn, sd->num_sms,
                                         reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {

@@ -38,11 +38,35 @@ bool pair_config_enabled() {
     return v == 1;
 }
 
+// splits: K slices (1 = none), or kStreamK: one pass whose ragged last wave is shared out by K blocks.
+constexpr int kStreamK = -1;
+
 struct GemmPlan {
     int block_n;
     int splits;
     double cost;
 };
+
+// RF_FP8_GEMM_STREAMK=1 makes every automatic plan whose tiles do not fill whole waves a stream-K plan, =0 never
+// uses stream-K; unset, the tuned table and the cost model decide.
+int streamk_override() {
+    static int v = -2;
+    if (v == -2) {
+        const char* e = getenv("RF_FP8_GEMM_STREAMK");
+        v = e ? (atoi(e) != 0 ? 1 : 0) : -1;
+    }
+    return v;
+}
+
+// Tiles of the stream-K region of this launch, 0 = the plan runs as a plain pass.
+int streamk_region(int m, int n, int k, int bn, int num_sms) {
+    if (rf::gemm_is_pair(bn)) return 0;
+    const int tiles = ((m + 127) / 128) * ((n + bn - 1) / bn);
+    const int sk = rf::gemm_streamk_tiles(tiles, num_sms);
+    // shares shorter than two K blocks are all fix-up and no work
+    if (sk > 0 && (long long)sk * (k / kBlockK) < 2LL * num_sms) return 0;
+    return sk;
+}
 
 // Cost model, in units of one 128-deep K block of a 128 x 128 tile at full tensor rate
 // (about 0.14 us): rounds of tiles over the SMs x (K blocks per slice + fixed per-tile cost),
@@ -73,7 +97,7 @@ GemmPlan plan_for(int m, int n, int k, int num_sms, int bn, int forced_split) {
     return best;
 }
 
-GemmPlan choose_plan(int m, int n, int k, int num_sms, int forced_split) {
+GemmPlan choose_plan_inner(int m, int n, int k, int num_sms, int forced_split) {
     const int fb = forced_block_n();
     if (fb) return plan_for(m, n, k, num_sms, fb, forced_split);
     // a measured entry for this exact shape beats the model (the caller's explicit split still wins)
@@ -88,7 +112,38 @@ GemmPlan choose_plan(int m, int n, int k, int num_sms, int forced_split) {
         GemmPlan pp = plan_for(m, n, k, num_sms, 512, forced_split);
         if (pp.cost < best.cost) best = pp;
     }
+    // Stream-K instead of a plain single pass, in K blocks of the chosen tile: a plain pass takes
+    // rounds x (kb + per-tile cost), a stream-K pass the even share of all K blocks plus its fixed cost (slot
+    // write, slot read, one more piece per CTA: 7-11 us measured on B200, about 18 K blocks of a 128 x 256 tile).
+    // That pays when a long-K shape has just over a whole number of waves (160 tiles of 56 K blocks: 2 x 56
+    // against 60.5 + 18); none of the 18 benchmark shapes is such a shape.
+    if (forced_split == 0 && best.splits == 1 && !rf::gemm_is_pair(best.block_n) &&
+        streamk_region(m, n, k, best.block_n, num_sms) > 0) {
+        const int kb = k / kBlockK;
+        const int tiles = ((m + 127) / 128) * ((n + best.block_n - 1) / best.block_n);
+        const int rounds = (tiles + num_sms - 1) / num_sms;
+        const double plain = (double)rounds * (kb + 3.0);
+        const double shared = (double)tiles * kb / num_sms + 3.0 * (tiles / num_sms + 1) + 18.0;
+        if (shared < plain) best.splits = kStreamK;
+    }
     return best;
+}
+
+// forced_split: > 0 = that many K slices, kStreamK = stream-K, 0 = the library's choice.
+GemmPlan choose_plan(int m, int n, int k, int num_sms, int forced_split) {
+    GemmPlan plan = choose_plan_inner(m, n, k, num_sms, forced_split == kStreamK ? 1 : forced_split);
+    if (forced_split == kStreamK) plan.splits = kStreamK;
+    if (forced_split == 0) {
+        const int ov = streamk_override();
+        if (ov == 1) {
+            if (plan.splits != kStreamK) plan = GemmPlan{forced_block_n() ? plan.block_n : 256, kStreamK, 0.0};
+        } else if (ov == 0 && plan.splits == kStreamK) {
+            plan.splits = 1;
+        }
+    }
+    // a stream-K plan that has no ragged wave to share out is a plain pass
+    if (plan.splits == kStreamK && streamk_region(m, n, k, plan.block_n, num_sms) == 0) plan.splits = 1;
+    return plan;
 }
 
 // `dest_c` / `n_dest` / `dest_n` / `col_offset`: when n_dest > 1 the [m, n] result is written at column
@@ -115,14 +170,18 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
 
     const int kb = k / kBlockK;
     if (split_k > kb) split_k = kb;
+    if (split_k < kStreamK) return RF_ERR_BAD_SHAPE;
     GemmPlan plan = choose_plan(m, n, k, st->num_sms, split_k);
-    if (mn_major && rf::gemm_is_pair(plan.block_n)) plan = plan_for(m, n, k, st->num_sms, 256, split_k);
+    if (mn_major && rf::gemm_is_pair(plan.block_n)) plan = plan_for(m, n, k, st->num_sms, 256, split_k > 0 ? split_k : 0);
+    // stream-K serves the row-major single-destination GEMM; elsewhere such a plan runs as a plain pass
+    if (plan.splits == kStreamK && (mn_major || n_dest > 1 || rf::gemm_is_pair(plan.block_n))) plan.splits = 1;
     const int bn = plan.block_n;
-    const int splits = plan.splits;
+    const int sk_tiles = plan.splits == kStreamK ? streamk_region(m, n, k, bn, st->num_sms) : 0;
+    const int splits = plan.splits == kStreamK ? 1 : plan.splits;
 
     float* partial = nullptr;
-    if (splits > 1) {
-        const size_t need = (size_t)splits * m * n * sizeof(float);
+    if (splits > 1 || sk_tiles > 0) {
+        const size_t need = sk_tiles > 0 ? rf::gemm_streamk_bytes(bn, st->num_sms) : (size_t)splits * m * n * sizeof(float);
         if (own_workspace) {
             partial = static_cast<float*>(rf::device_scratch(need));
             if (!partial) return RF_ERR_CUDA;
@@ -182,8 +241,11 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
     }
     p.n_dest = n_dest;
     p.c_col_offset = col_offset;
-    p.fnuz_flags = nullptr;
     p.dest_first = (n_dest > 1 && dest_n > 0 && n > 0) ? (col_offset / n) % n_dest : 0;   // = rank for an N-split
+    if (sk_tiles > 0) {
+        p.sk_tiles = sk_tiles;
+        p.sk_token = rf::gemm_streamk_token(rf::next_streamk_epoch());
+    }
     rf::GemmDestMaps dests;
     bool use_dests = false;
     if (fnuz) {
@@ -282,12 +344,32 @@ int rf_fp8_gemm_choose_split(int m, int n, int k) {
     return choose_plan(m, n, k, st->num_sms, 0).splits;
 }
 
-size_t rf_fp8_gemm_workspace_bytes(int m, int n, int k, int split_k) {
-    if (!shape_ok(m, n, k)) return 0;
-    int s = split_k > 0 ? split_k : rf_fp8_gemm_choose_split(m, n, k);
+int rf_fp8_gemm_work_pieces(int m, int n, int k, int block_n, int split_k, int num_sms, int cta, int* pieces,
+                            int max_pieces) {
+    if (!shape_ok(m, n, k) || (block_n != 128 && block_n != 256) || num_sms < 1 || cta < 0 || !pieces) return -1;
     const int kb = k / kBlockK;
-    if (s > kb) s = kb;
-    return s > 1 ? (size_t)s * m * n * sizeof(float) : 0;
+    if (split_k < kStreamK || split_k == 0 || split_k > kb) return -1;
+    rf::GemmParams p;
+    p.k = k;
+    p.tiles_m = (m + 127) / 128;
+    p.tiles_n = (n + block_n - 1) / block_n;
+    p.splits = split_k == kStreamK ? 1 : split_k;
+    p.sk_tiles = split_k == kStreamK ? rf::gemm_streamk_tiles(p.tiles_m * p.tiles_n, num_sms) : 0;
+    const int total = p.tiles_m * p.tiles_n * p.splits;
+    const int grid = (total < num_sms && p.sk_tiles == 0) ? total : num_sms;
+    if (cta >= grid) return 0;
+    return rf::fp8_gemm_walk_pieces(p, cta, grid, pieces, max_pieces);
+}
+
+size_t rf_fp8_gemm_workspace_bytes(int m, int n, int k, int split_k) {
+    if (!shape_ok(m, n, k) || split_k < kStreamK) return 0;
+    rf::DeviceState* st = rf::device_state();
+    const int num_sms = st ? st->num_sms : 148;      // (no GPU: the answer for a B200)
+    const int kb = k / kBlockK;
+    if (split_k > kb) split_k = kb;
+    const GemmPlan plan = choose_plan(m, n, k, num_sms, split_k);
+    if (plan.splits == kStreamK) return rf::gemm_streamk_bytes(plan.block_n, num_sms);
+    return plan.splits > 1 ? (size_t)plan.splits * m * n * sizeof(float) : 0;
 }
 
 int rf_fp8_gemm(const void* a, const void* b, const float* as, const float* bs, void* c, int m, int n, int k,

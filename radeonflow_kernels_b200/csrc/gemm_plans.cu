@@ -2,7 +2,7 @@
 //
 // The reference picks its kernel instance from a compile-time dispatch table that an offline brute-force
 // tuner regenerates (src/gemm/gemm_launcher.cpp:229-247, tuner/gemm_tuner.py:343-385).  Here the kernels are
-// shape-generic, so the table only has to hold (tile width, split-K) per shape and can be changed at run
+// shape-generic, so the table only has to hold (tile width, split-K or -1 for stream-K) per shape and can be changed at run
 // time: a built-in table measured on B200 for the benchmark shapes, entries registered by the caller
 // (rf_fp8_gemm_set_plan), and a text file (rf_fp8_gemm_load_plans, or RF_FP8_GEMM_PLANS at first use)
 // written by `python -m radeonflow_kernels_b200.tune`.
@@ -39,7 +39,7 @@ const int kBuiltin[][5] = {
 bool entry_valid(int m, int n, int k, int block_n, int splits) {
     if (m <= 0 || n <= 0 || k <= 0 || (n % 64) != 0 || (k % 128) != 0) return false;
     if (block_n != 128 && block_n != 256 && block_n != 512) return false;
-    return splits >= 1 && splits <= k / 128 && splits <= 64;
+    return splits == -1 || (splits >= 1 && splits <= k / 128 && splits <= 64);     // -1 = stream-K
 }
 
 int load_file_locked(const char* path) {

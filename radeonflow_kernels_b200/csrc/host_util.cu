@@ -50,6 +50,13 @@ int next_launch_tag() {
     return (int)(counter.fetch_add(1, std::memory_order_relaxed) % (unsigned)kStatusTagMask) + 1;
 }
 
+unsigned next_streamk_epoch() {
+    static std::atomic<unsigned> counter{0};
+    unsigned v;
+    do v = counter.fetch_add(1, std::memory_order_relaxed) + 1; while (v == 0);
+    return v;
+}
+
 void* device_scratch(size_t bytes, int slot) {
     DeviceState* st = device_state();
     if (!st || slot < 0 || slot >= kScratchSlots) return nullptr;

@@ -23,7 +23,7 @@ struct DeviceState {
 
 
 enum ScratchSlot {
-    kScratchGemm = 0,      // split-K slices of the FP8 GEMM
+    kScratchGemm = 0,      // split-K slices / stream-K slots and flags of the FP8 GEMM
     kScratchMoeAux = 1,    // MoE tile lists and sort counters
     kScratchMoeWork = 2,   // MoE intermediates handed out by initialize_workspace
     kScratchFnuz = 3,      // e4m3fn copies of e4m3fnuz operands (reference-format GEMM entry)
@@ -36,6 +36,9 @@ DeviceState* device_state();
 
 // A fresh tag (1 .. kStatusTagMask) for the next kernel launch that records expired waits.
 int next_launch_tag();
+
+// A fresh non-zero number for the flags of the next stream-K launch (flags that carry another number are stale).
+unsigned next_streamk_epoch();
 
 // Library-owned buffer `slot` of at least `bytes` on the current device (grows by
 // freeing and re-allocating; synchronises the device when it grows).

@@ -113,6 +113,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     }
 }
 
+// ------------------------------------------------------ flags between CTAs --
+__device__ __forceinline__ void st_release_gpu_u64(unsigned long long* flag, unsigned long long v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(flag), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long* flag) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+    return v;
+}
+// Bounded wait for *flag == want (same limit, status word and unwinding rule as mbar_wait).
+__device__ __forceinline__ bool flag_wait_u64(const unsigned long long* flag, unsigned long long want, int* status,
+                                              int code, int tag) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 1;; ++it) {
+        if (ld_acquire_gpu_u64(flag) == want) return true;
+        if ((it & 0x3fu) == 0) {
+            const int seen = *reinterpret_cast<volatile int*>(status);
+            if (seen != 0 && (seen >> kStatusTagShift) == tag) return false;
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > wait_limit_ns(status)) {
+                atomicCAS(status, 0, code | (tag << kStatusTagShift));
+                return false;
+            }
+        }
+    }
+}
+
 // ----------------------------------------------- programmatic dependent launch --
 // A kernel launched with the programmatic-stream-serialization attribute may start while the kernel
 // before it in the stream is still running.  griddep_wait() blocks until that kernel has completed and

@@ -1,11 +1,11 @@
-"""Offline tuner of the FP8 GEMM plan table (tile width x split-K per shape).
+"""Offline tuner of the FP8 GEMM plan table (tile width x split-K or stream-K per shape).
 
     python -m radeonflow_kernels_b200.tune [--shapes MxNxK,...] [--out plans.txt] [--emit-inc FILE] [--pair]
 
 The B200 analogue of the reference's brute-force tuner (tuner/gemm_tuner.py:317-549 enumerates kernel
 parameterisations, compiles and times each; tuner/gemm_batch.py:8-27 walks the benchmark shapes) and of
 the dispatch table it regenerates (src/gemm/gemm_launcher.cpp:229-247).  The kernels here are
-shape-generic, so nothing is compiled: every candidate (tile width, split-K) is registered through
+shape-generic, so nothing is compiled: every candidate (tile width, split-K or stream-K) is registered through
 `rf_fp8_gemm_set_plan`, timed as a CUDA graph of launches that rotate over operand sets larger than L2
 (3 warm-up replays, 5 timed, median; the reference template times 3 + 10 launches,
 tuner/template/gemm_perf.cpp:62-81) and the fastest is written out as "m n k block_n split_k".
@@ -20,11 +20,13 @@ import sys
 NK_PAIRS = [(1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
             (512, 7168), (4096, 512)]
 BENCHMARK_SHAPES = [(m, n, k) for m in (1024, 6144) for (n, k) in NK_PAIRS]
+STREAM_K = -1       # RF_SPLIT_STREAMK of include/rf_b200.h
 
 
 def candidates(m, n, k, num_sms=148, pair=False):
     """(block_n, split_k) pairs worth timing: both tile widths; split-K only while the tiles do not
-    fill the SMs and every slice keeps at least two K blocks."""
+    fill the SMs and every slice keeps at least two K blocks; stream-K (split_k = -1) when the tiles leave a
+    ragged last wave and every SM's share is at least two K blocks."""
     kb = k // 128
     out = []
     for bn in (128, 256) + ((512,) if pair else ()):
@@ -33,6 +35,8 @@ def candidates(m, n, k, num_sms=148, pair=False):
         tiles = -(-m // rows) * -(-n // cols)
         units = num_sms // 2 if bn == 512 else num_sms
         out.append((bn, 1))
+        if bn != 512 and tiles % units != 0 and min(tiles, tiles % units + units) * kb >= 2 * units:
+            out.append((bn, STREAM_K))
         for s in (2, 3, 4, 6, 8):
             if tiles * (s - 1) >= units or kb // s < 2:
                 break

@@ -91,6 +91,89 @@ def test_split_k_agrees_with_oracle(split):
     assert_close(run_gemm(a, b, a_s, b_s, split_k=split), o.fp8_gemm(a, b, a_s, b_s))
 
 
+# stream-K (split_k = -1): ragged last waves of the benchmark shapes, ragged M and N, a region smaller than one wave
+# whose tiles are each shared by several CTAs, and one tile shared by all 148 CTAs (147 partial sums added in order)
+STREAMK_SHAPES = [(1024, 7168, 2048, 5), (1024, 3072, 1536, 6), (6144, 512, 7168, 7), (6144, 7168, 2048, 8),
+                  (1000, 1600, 1024, 9), (300, 4160, 896, 10), (1024, 1536, 7168, 11), (128, 64, 128 * 300, 12),
+                  (4000, 4032, 384, 13)]
+
+
+@pytest.mark.parametrize("m,n,k,seed", STREAMK_SHAPES)
+def test_stream_k_agrees_with_oracle_and_is_deterministic(rf_lib, m, n, k, seed):
+    a, b, a_s, b_s = o.generate_input(m, n, k, seed, "randn")
+    da, db, das, dbs = gemm_device_inputs(a, b, a_s, b_s)
+    need = rf_lib.rf_fp8_gemm_workspace_bytes(m, n, k, -1)
+    assert need > 0, "these shapes leave a ragged wave: the plan must be a stream-K pass"
+    runs = []
+    for rep in range(2):
+        full, c = canary_output(m, n)
+        # scratch with arbitrary old content: stale flags and slots must not matter
+        ws = torch.randint(0, 255, (need,), dtype=torch.uint8, device="cuda:0")
+        G.fp8_mm(da, db, das, dbs, c, split_k=-1, workspace=ws)
+        torch.cuda.synchronize()
+        assert G.device_status() == 0, "a bounded device-side wait expired"
+        assert canary_intact(full, m, n)
+        runs.append(c.view(torch.uint16).cpu().numpy())
+    assert np.array_equal(runs[0], runs[1]), "partial sums are added in a fixed order: same bits every run"
+    assert_close(runs[0], o.fp8_gemm(a, b, a_s, b_s))
+    # too little scratch is refused on the host
+    small = torch.empty(need - 256, dtype=torch.uint8, device="cuda:0")
+    st = rf_lib.rf_fp8_gemm(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(), c.data_ptr(), m, n, k, -1,
+                            small.data_ptr(), small.numel(), None)
+    assert st == 4          # RF_ERR_WORKSPACE
+
+
+def test_stream_k_back_to_back_launches_share_one_scratch(rf_lib):
+    """Consecutive launches reuse slots and flags without clearing: each launch's flags carry its own number."""
+    shapes = [(1024, 7168, 2048), (1024, 3072, 1536), (1024, 7168, 2048)]
+    need = max(rf_lib.rf_fp8_gemm_workspace_bytes(m, n, k, -1) for (m, n, k) in shapes)
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda:0")
+    cases = []
+    for i, (m, n, k) in enumerate(shapes):
+        a, b, a_s, b_s = o.generate_input(m, n, k, 30 + i, "randn")
+        cases.append((a, b, a_s, b_s, gemm_device_inputs(a, b, a_s, b_s), torch.empty((m, n), dtype=torch.bfloat16,
+                                                                                     device="cuda:0")))
+    for _ in range(3):
+        for (a, b, a_s, b_s, dev, c) in cases:
+            G.fp8_mm(*dev, c, split_k=-1, workspace=ws)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    for (a, b, a_s, b_s, dev, c) in cases:
+        assert_close(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a, b, a_s, b_s))
+
+
+def test_stream_k_in_a_replayed_graph(rf_lib):
+    """A captured launch carries the same flag number at every replay, so the flags must come back cleared: the
+    owner clears what it consumed.  Operands change between replays; a stale flag would let an owner read the
+    previous replay's partial sums (or half-written ones)."""
+    m, n, k = 1024, 3072, 1536
+    need = rf_lib.rf_fp8_gemm_workspace_bytes(m, n, k, -1)
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda:0")
+    a, b, a_s, b_s = o.generate_input(m, n, k, 50, "randn")
+    da, db, das, dbs = gemm_device_inputs(a, b, a_s, b_s)
+    c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda:0")
+    side = torch.cuda.Stream()
+    G.fp8_mm(da, db, das, dbs, c, split_k=-1, workspace=ws)          # first use outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            G.fp8_mm(da, db, das, dbs, c, split_k=-1, workspace=ws)
+            G.fp8_mm(da, db, das, dbs, c, split_k=-1, workspace=ws)
+    for seed in (51, 52, 53):
+        a, b, a_s, b_s = o.generate_input(m, n, k, seed, "randn")
+        for dst, src in zip((da, db, das, dbs), gemm_device_inputs(a, b, a_s, b_s)):
+            dst.copy_(src)
+        c.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert G.device_status() == 0
+        assert_close(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a, b, a_s, b_s))
+    # nothing is left raised
+    flags = ws[148 * 128 * 256 * 4:].view(torch.int64)
+    assert int(flags.abs().sum().item()) == 0
+
+
 @pytest.mark.parametrize("m", [1, 7, 33, 127, 129, 200, 255, 257])
 def test_ragged_m(m):
     a, b, a_s, b_s = o.generate_input(m, 192, 384, 5 + m, "randn")

@@ -34,7 +34,7 @@ def test_invalid_entries_are_rejected(rf_lib):
 def test_builtin_table_covers_the_benchmark_shapes(rf_lib):
     for (m, n, k) in tune.BENCHMARK_SHAPES:
         bn, s = _get(rf_lib, m, n, k)
-        assert bn in (128, 256, 512) and 1 <= s <= k // 128
+        assert bn in (128, 256, 512) and (1 <= s <= k // 128 or s == tune.STREAM_K)
 
 
 def test_load_plans_file(rf_lib, tmp_path):
@@ -55,8 +55,10 @@ def test_load_plans_file(rf_lib, tmp_path):
 def test_tuner_candidates():
     c = tune.candidates(1024, 512, 7168)
     assert (128, 1) in c and (256, 1) in c and (128, 4) in c
-    assert all(s == 1 for (_, s) in tune.candidates(6144, 7168, 2048))     # tiles already fill the SMs
-    assert all(7168 // 128 // s >= 2 for (_, s) in c)
+    # tiles already fill the SMs: no split-K, but the ragged last wave (1344 tiles = 9.08 x 148) makes stream-K a candidate
+    assert sorted(set(s for (_, s) in tune.candidates(6144, 7168, 2048))) == [tune.STREAM_K, 1]
+    assert all(s == 1 for (_, s) in tune.candidates(128 * 148, 256, 1024))   # whole waves: nothing to share out
+    assert all(s == tune.STREAM_K or 7168 // 128 // s >= 2 for (_, s) in c)
     assert (512, 1) in tune.candidates(6144, 4608, 7168, pair=True)
     assert tune.parse_shapes("64x128x256,1024X576x7168") == [(64, 128, 256), (1024, 576, 7168)]
 
@@ -81,6 +83,26 @@ def test_registered_plan_is_used_and_correct(rf_lib, bn, split):
         assert G.device_status() == 0
         ok, n_bad, max_err = o.check(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a, b, a_s, b_s))
         assert ok, (n_bad, max_err)
+    finally:
+        rf_lib.rf_fp8_gemm_set_plan(m, n, k, 0, 0)
+
+
+def test_stream_k_plan_entry(rf_lib):
+    """A stream-K table entry is honoured where there is a ragged wave worth sharing out, and degrades to the plain
+    pass where there is not (whole waves, or shares shorter than two K blocks)."""
+    m, n, k = 1088, 3072, 1536                       # 9 x 12 = 108 tiles of 12 K blocks on 148 SMs
+    assert rf_lib.rf_fp8_gemm_set_plan(m, n, k, 256, tune.STREAM_K) == 0
+    try:
+        assert _get(rf_lib, m, n, k) == (256, tune.STREAM_K)
+        assert rf_lib.rf_fp8_gemm_workspace_bytes(m, n, k, 0) == 148 * (128 * 256 * 4 + 8)
+        assert rf_lib.rf_fp8_gemm_workspace_bytes(m, n, k, 2) == 2 * m * n * 4       # an explicit split still wins
+    finally:
+        rf_lib.rf_fp8_gemm_set_plan(m, n, k, 0, 0)
+    m, n, k = 384, 576, 1024                         # 15 tiles x 8 K blocks: less than two K blocks per SM
+    assert rf_lib.rf_fp8_gemm_set_plan(m, n, k, 128, tune.STREAM_K) == 0
+    try:
+        assert _get(rf_lib, m, n, k) == (128, 1)
+        assert rf_lib.rf_fp8_gemm_workspace_bytes(m, n, k, 0) == 0
     finally:
         rf_lib.rf_fp8_gemm_set_plan(m, n, k, 0, 0)
 

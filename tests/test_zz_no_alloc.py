@@ -27,7 +27,7 @@ def run_both(rf_lib, m, n, k, split, seed):
     st = rf_lib.rf_fp8_gemm_static_scratch(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(),
                                            c_new.data_ptr(), m, n, k, split, None)
     assert st == 0
-    ws = torch.empty(split * m * n * 4, dtype=torch.uint8, device="cuda:0")
+    ws = torch.empty(max(16, rf_lib.rf_fp8_gemm_workspace_bytes(m, n, k, split)), dtype=torch.uint8, device="cuda:0")
     st = rf_lib.rf_fp8_gemm(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(), c_old.data_ptr(), m, n, k,
                             split, ws.data_ptr(), ws.numel(), None)
     assert st == 0
@@ -49,6 +49,9 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point(rf_lib):
     run_both(rf_lib, 1024, 512, 7168, 7, seed=1)       # 7 slices x 2 MiB = 14 MiB of the 16 MiB
     run_both(rf_lib, 320, 576, 2304, 3, seed=2)
     run_both(rf_lib, 256, 192, 1024, 1, seed=3)        # no scratch needed
+    # stream-K through the built-in array: 128-wide tiles, 148 slots of 64 KiB and their flags
+    assert 0 < rf_lib.rf_fp8_gemm_workspace_bytes(1024, 576, 7168, -1) <= STATIC_BYTES
+    run_both(rf_lib, 1024, 576, 7168, -1, seed=4)
 
 
 def test_automatic_split_never_exceeds_the_built_in_array(rf_lib):
