@@ -317,6 +317,27 @@ def make_moe_weights(torch, dev, d, f, experts, seed, with_router_for=None):
     return w
 
 
+def measure_write_gbs(torch, dev):
+    """Yardstick only: GB/s of a device memset over 1 GiB (best of 10).  HBM takes writes at about half the rate of
+    the read+write copy the roofline's `peak` comes from, so a kernel whose traffic is mostly its bf16 result
+    (the K <= 512 shapes) is bounded by this figure, not by the copy figure."""
+    buf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        buf.zero_()
+    torch.cuda.synchronize()
+    best = 0.0
+    for _ in range(10):
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        buf.zero_()
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, buf.numel() / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    del buf
+    return best
+
+
 def measure_fp8_peak(torch, dev):
     """Yardstick only: a plain (unscaled-block) FP8 GEMM of the vendor library, e4m3 8192^3 through
     torch._scaled_mm, best of 10 after warm-up, in TFLOP/s.  None when the call is not available."""
@@ -750,6 +771,7 @@ def run_gpu_arm(args):
     fp8_assumed = 2.0 * peaks["bf16_tflops"]
     fp8_peak = fp8_measured if fp8_measured else fp8_assumed
     peaks["fp8_tflops"] = fp8_peak
+    write_gbs = measure_write_gbs(torch, dev)
     per_shape = []
     for s in shapes:
         m, n, k = s["m"], s["n"], s["k"]
@@ -785,6 +807,9 @@ def run_gpu_arm(args):
             "gbs": round(by / us / 1e3, 1), "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 3),
             # the shape's own bound: the slower of its tensor time and its HBM time, over the measured time
             "frac_of_bound": round(max(fl / (fp8_peak * 1e6), by / (peaks["hbm_gbs"] * 1e3)) / us, 3),
+            # the same with the result's write time at the measured write-only rate as a third bound
+            "frac_of_bound_with_write": round(max(fl / (fp8_peak * 1e6), by / (peaks["hbm_gbs"] * 1e3),
+                                                  2.0 * m * n / (write_gbs * 1e3)) / us, 3),
             "rotating_sets": reps,
         })
         del sets, g2
@@ -883,6 +908,9 @@ def run_gpu_arm(args):
                                          "measured in this run as a yardstick" if fp8_measured else
                                          f"2 x bf16_tflops of {peaks['source']} (FP8 yardstick GEMM unavailable)"),
                          "peak_2x_bf16_burst": fp8_assumed,
+                         "hbm_write_only_gbs": round(write_gbs, 1),
+                         "hbm_write_only_note": "device memset of 1 GiB measured in this run; the third bound of the "
+                                                "per-shape frac_of_bound_with_write (result bytes / this rate)",
                          "kernel": "fp8_gemm_kernel"},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
