@@ -48,7 +48,8 @@ SWEEP = [(m, n, k) for m in (1024, 6144) for (n, k) in NK_PAIRS]
 # ncu pass (two DRAM counters, --clock-control none, caches flushed before each measured launch) over the fifth
 # sweep of `bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-extras`, taken with the kernel as it is now.
 # Reads = A + B + scales once; C mostly stays in the 126 MB L2 at kernel end, hence traffic < algorithmic.
-NCU_DRAM_BYTES = [18641920, 6395648, 11742464, 2162176, 16900608, 40662272, 19006464, 11282944, 2694400, 57062912, 14552832, 49679360, 29924608, 61005824, 115116800, 65865984, 49142272, 5400832]
+NCU_DRAM_BYTES = [18641920, 6396416, 11742720, 2162176, 16901376, 40663040, 19006976, 11283200, 2694144, 56805376,
+                  14512128, 49635072, 30227455, 60430336, 112845824, 65882623, 49146879, 5460736]
 # same two counters for the largest moe_gemm_kernel launch of the single-GPU MoE layer (routed fc1)
 MOE_NCU_DRAM_BYTES = 2.91e9
 METRIC = "fp8_blockscaled_gemm_tflops"
