@@ -67,7 +67,7 @@ void run(void *a, void *b, void *as, void *bs, void *c, int m, int n, int k, Per
 /* Status-returning twin of `run` with caller-provided scratch.
  * `workspace` may be NULL when rf_fp8_gemm_workspace_bytes() returns 0 for the
  * shape; otherwise it must hold at least that many bytes (256-byte aligned).
- * `split_k` = 0 lets the library choose; >= 1 forces that many K slices
+ * `split_k` = 0 lets the library choose; >= 1 forces that many K slices (at most 64, and at most k/128)
  * (reference: compile-time SPLITK_FACTOR, src/gemm/gemm_launcher.cpp:229-247);
  * RF_SPLIT_STREAMK (-1) asks for one pass whose ragged last wave of tiles is
  * shared out over all SMs by K blocks ("stream-K": the partial sums of a tile

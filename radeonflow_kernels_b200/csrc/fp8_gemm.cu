@@ -118,14 +118,23 @@ struct TileCoord {
 // Tile number -> tile.  Consecutive tiles walk down M inside a band of GROUP_M row blocks before moving to
 // the next column block, so the CTAs that run concurrently share B tiles (and A bands) in L2.
 __device__ __forceinline__ TileCoord decode_tile(int tile, int tiles_m, int tiles_n) {
+    // (This runs once per tile in every role, on the epilogue's critical path between two tiles: one integer
+    // division, and shifts for the full bands.  Measured: the earlier form with five divisions, together with two
+    // 64-bit divisions for the K range, cost the epilogue about 1400 cycles per tile, the present one 600.)
     constexpr int GROUP_M = 8;
     TileCoord t;
-    int band = tile / (GROUP_M * tiles_n);
-    int first_m = band * GROUP_M;
-    int band_rows = min(GROUP_M, tiles_m - first_m);
-    int in_band = tile - band * GROUP_M * tiles_n;
-    t.m_blk = first_m + in_band % band_rows;
-    t.n_blk = in_band / band_rows;
+    const int group = GROUP_M * tiles_n;
+    const int band = tile / group;
+    const int first_m = band * GROUP_M;
+    const int band_rows = min(GROUP_M, tiles_m - first_m);
+    const int in_band = tile - band * group;
+    if (band_rows == GROUP_M) {
+        t.m_blk = first_m + (in_band & (GROUP_M - 1));
+        t.n_blk = in_band >> 3;
+    } else {
+        t.n_blk = in_band / band_rows;
+        t.m_blk = first_m + in_band - t.n_blk * band_rows;
+    }
     return t;
 }
 
@@ -178,10 +187,16 @@ struct WorkWalker<false> {
     __host__ __device__ __forceinline__ bool next(Piece& pc, const GemmParams& p, int n_units, int kb_total) {
         w += n_units;
         if (w >= p.tiles_m * p.tiles_n * p.splits) return false;
-        const int split = w % p.splits;
         pc.item = w;
-        pc.kb0 = (int)((long long)kb_total * split / p.splits);
-        pc.kb1 = (int)((long long)kb_total * (split + 1) / p.splits);
+        if (p.splits == 1) {
+            pc.kb0 = 0;
+            pc.kb1 = kb_total;
+        } else {
+            // (k / 128 < 2^24 and splits <= 64: the products fit 32 bits)
+            const int split = w % p.splits;
+            pc.kb0 = kb_total * split / p.splits;
+            pc.kb1 = kb_total * (split + 1) / p.splits;
+        }
         return true;
     }
 };
@@ -327,7 +342,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         WorkWalker<STREAM_K> walk(p, unit, unit_stride, kb_total);
         Piece pc;
         while (ok && walk.next(pc, p, unit_stride, kb_total)) {
-            const TileCoord t = decode_tile(pc.item / p.splits, p.tiles_m, p.tiles_n);
+            const TileCoord t = decode_tile(p.splits == 1 ? pc.item : pc.item / p.splits, p.tiles_m, p.tiles_n);
             // rows of A and of B this CTA fetches (a CTA pair splits both between its two CTAs)
             const int a_row0 = TWO ? (t.m_blk * 2 + (int)cta_rank) * BM : t.m_blk * BM;
             const int b_row0 = t.n_blk * BN + (TWO ? (int)cta_rank * Cfg::kBRows : 0);
@@ -510,7 +525,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         const float* as_row = p.a_scale;
         const float* bs_row = p.b_scale;
         auto begin_piece = [&](const Piece& pc) {
-            const TileCoord t = decode_tile(pc.item / p.splits, p.tiles_m, p.tiles_n);
+            const TileCoord t = decode_tile(p.splits == 1 ? pc.item : pc.item / p.splits, p.tiles_m, p.tiles_n);
             kb0 = pc.kb0;
             kb1 = pc.kb1;
             const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
@@ -693,7 +708,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             // that global memory is written in whole 128-byte row segments.
             {
                 constexpr int SL = Cfg::kSlabs;
-                const TileCoord t = decode_tile(pc.item / p.splits, p.tiles_m, p.tiles_n);
+                const TileCoord t = decode_tile(p.splits == 1 ? pc.item : pc.item / p.splits, p.tiles_m, p.tiles_n);
                 const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
                 const int col0 = t.n_blk * BN + grp * CPT;
                 const uint32_t slab0 = slab_base + ew * SL * Cfg::kSlabBytes;

@@ -10,6 +10,7 @@
 namespace {
 
 constexpr int kBlockK = 128;
+constexpr int kMaxSplits = 64;     // K slices per GEMM (the kernel's 32-bit K-range arithmetic relies on it)
 
 bool shape_ok(int m, int n, int k) { return m > 0 && n > 0 && k > 0 && (n % 64) == 0 && (k % kBlockK) == 0; }
 
@@ -170,6 +171,7 @@ int gemm_impl(const void* a, const void* b, const float* as, const float* bs, vo
 
     const int kb = k / kBlockK;
     if (split_k > kb) split_k = kb;
+    if (split_k > kMaxSplits) split_k = kMaxSplits;
     if (split_k < kStreamK) return RF_ERR_BAD_SHAPE;
     GemmPlan plan = choose_plan(m, n, k, st->num_sms, split_k);
     if (mn_major && rf::gemm_is_pair(plan.block_n)) plan = plan_for(m, n, k, st->num_sms, 256, split_k > 0 ? split_k : 0);
@@ -295,6 +297,7 @@ namespace rf {
 void fp8_gemm_plan(int m, int n, int k, int num_sms, int split_k, int* block_n, int* splits) {
     const int kb = k / kBlockK;
     if (split_k > kb) split_k = kb;
+    if (split_k > kMaxSplits) split_k = kMaxSplits;
     const GemmPlan plan = choose_plan(m, n, k, num_sms, split_k);
     *block_n = plan.block_n;
     *splits = plan.splits;
@@ -348,7 +351,7 @@ int rf_fp8_gemm_work_pieces(int m, int n, int k, int block_n, int split_k, int n
                             int max_pieces) {
     if (!shape_ok(m, n, k) || (block_n != 128 && block_n != 256) || num_sms < 1 || cta < 0 || !pieces) return -1;
     const int kb = k / kBlockK;
-    if (split_k < kStreamK || split_k == 0 || split_k > kb) return -1;
+    if (split_k < kStreamK || split_k == 0 || split_k > kb || split_k > kMaxSplits) return -1;
     rf::GemmParams p;
     p.k = k;
     p.tiles_m = (m + 127) / 128;
@@ -367,6 +370,7 @@ size_t rf_fp8_gemm_workspace_bytes(int m, int n, int k, int split_k) {
     const int num_sms = st ? st->num_sms : 148;      // (no GPU: the answer for a B200)
     const int kb = k / kBlockK;
     if (split_k > kb) split_k = kb;
+    if (split_k > kMaxSplits) split_k = kMaxSplits;
     const GemmPlan plan = choose_plan(m, n, k, num_sms, split_k);
     if (plan.splits == kStreamK) return rf::gemm_streamk_bytes(plan.block_n, num_sms);
     return plan.splits > 1 ? (size_t)plan.splits * m * n * sizeof(float) : 0;
