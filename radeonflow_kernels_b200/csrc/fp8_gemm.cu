@@ -540,10 +540,19 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 qb[d] = __ldg(bs_row + kk * bs_ks);
             }
         };
+        // The next piece is drawn (tile decoded, scale pointers set, first scales requested) in the middle of the
+        // current tile's store, between its first and second chunk, where the warp would otherwise wait for the
+        // TMA to have read the slab it is about to rewrite (about 240 cycles per chunk, measured).
         WorkWalker<STREAM_K> walk(p, unit, unit_stride, kb_total);
         Piece pc;
-        while (ok && walk.next(pc, p, unit_stride, kb_total)) {
-            begin_piece(pc);
+        bool have = walk.next(pc, p, unit_stride, kb_total);
+        if (have) begin_piece(pc);
+        auto advance = [&] {
+            have = walk.next(pc, p, unit_stride, kb_total);
+            if (have) begin_piece(pc);
+        };
+        while (ok && have) {
+            const int cur_item = pc.item;     // `pc` moves on to the next piece during the store
             float2 acc[CPT / 2];
             bool fresh = true;        // the accumulators still have to be cleared
             if (STREAM_K && kb0 > 0 && kb1 == kb_total) {
@@ -702,16 +711,21 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sk_stored_bar);
                 RF_STAT_END(w_skw);
+                advance();
                 continue;
             }
             // Tile store: each warp stages its 32 rows x 128 bytes in its own swizzled shared-memory slab, so
             // that global memory is written in whole 128-byte row segments.
             {
                 constexpr int SL = Cfg::kSlabs;
-                const TileCoord t = decode_tile(p.splits == 1 ? pc.item : pc.item / p.splits, p.tiles_m, p.tiles_n);
+                const TileCoord t = decode_tile(p.splits == 1 ? cur_item : cur_item / p.splits, p.tiles_m, p.tiles_n);
                 const int cta_m_blk = TWO ? t.m_blk * 2 + (int)cta_rank : t.m_blk;
                 const int col0 = t.n_blk * BN + grp * CPT;
                 const uint32_t slab0 = slab_base + ew * SL * Cfg::kSlabBytes;
+                // (128-wide tiles hold 64 accumulators per thread and store one chunk, or two short fp32 ones:
+                // measured, drawing the next piece in between makes them slower, so they draw it afterwards)
+                constexpr bool kAdvanceMidStore = CPT == 128;
+                bool advanced = false;
                 const int slab_row0 = cta_m_blk * BM + quad * 32;
                 // One lane hands the slab to the TMA, which clips rows >= m / columns >= n.  Consecutive stores of
                 // this warp alternate over its kSlabs slabs (n_stores counts them across tiles, so skipped chunks
@@ -752,8 +766,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                             }
                             tma_store_commit();
                         }
+                        if (kAdvanceMidStore && ch == 0) {
+                            advance();
+                            advanced = true;
+                        }
                     }
                 } else {
+                    const int cur_split = cur_item % p.splits;
 #pragma unroll
                     for (int ch = 0; ch < CPT / 32; ++ch) {
                         if (col0 + ch * 32 >= p.n) break;
@@ -772,11 +791,16 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_3d(&tma_p, slab, col0 + ch * 32, slab_row0, pc.item % p.splits);
+                            tma_store_3d(&tma_p, slab, col0 + ch * 32, slab_row0, cur_split);
                             tma_store_commit();
+                        }
+                        if (kAdvanceMidStore && ch == 0) {
+                            advance();
+                            advanced = true;
                         }
                     }
                 }
+                if (!advanced) advance();
             }
         }
         // Before exit the warp's slab must have been read by its last store.  Waiting for the writes themselves
