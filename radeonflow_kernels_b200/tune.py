@@ -125,7 +125,8 @@ def write_plans(table, path):
 
 def write_inc(table, path):
     with open(path, "w") as f:
-        f.write("// {m, n, k, tile width, split-K}; regenerate with `python -m radeonflow_kernels_b200.tune --emit-inc`.\n")
+        f.write("// {m, n, k, tile width, split-K (-1 = stream-K)}; regenerate with "
+                "`python -m radeonflow_kernels_b200.tune --emit-inc`.\n")
         for (m, n, k, bn, s, us) in table:
             f.write(f"{{{m}, {n}, {k}, {bn}, {s}}},   // {us:.2f} us\n")
 
