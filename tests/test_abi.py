@@ -56,6 +56,10 @@ def test_bad_arguments_are_rejected_on_the_host(rf_lib):
     assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 128, 1024, 4) == 4 * 128 * 128 * 4
     assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 128, 1024, 1) == 0
     assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 100, 1024, 4) == 0
+    # at most 64 K slices, and at most one per K block
+    assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 128, 128 * 100, 100) == 64 * 128 * 128 * 4
+    assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 128, 1024, 100) == 8 * 128 * 128 * 4
+    assert rf_lib.rf_fp8_gemm_workspace_bytes(128, 128, 1024, -2) == 0      # below RF_SPLIT_STREAMK: invalid
 
 
 def test_public_header_compiles_as_c_and_cpp(tmp_path):
