@@ -94,8 +94,8 @@ struct GemmCfg {
         STAGES * kStageBytes + kEpiWarps * kSlabs * kSlabBytes + kBarBytes + 1024;       // + alignment slack
     // The epilogue (64 or 128 accumulators per thread plus staging) wants more than the 168 registers a
     // 384-thread CTA starts with, the producer warpgroup far fewer: registers are rebalanced after set-up
-    // (128 * kRegsLo + 256 * kRegsHi <= 64512, the CTA's allocation at 168 per thread).  Measured on the
-    // 18-shape sweep: 120 / 192 is the fastest split for the default epilogue.
+    // (128 * kRegsLo + 256 * kRegsHi <= 64512, the CTA's allocation at 168 per thread).  The split is chosen by
+    // measurement on the 18-shape sweep.
     static constexpr bool kRebalanceRegs = true;
 #if defined(RF_REGS_LO) && defined(RF_REGS_HI)
     static constexpr int kRegsLo = RF_REGS_LO, kRegsHi = RF_REGS_HI;
@@ -103,7 +103,10 @@ struct GemmCfg {
     static constexpr int kRegsLo = kColsPerThread > 64 ? 40 : 104;
     static constexpr int kRegsHi = kColsPerThread > 64 ? 232 : 200;
 #else
-    static constexpr int kRegsLo = 120, kRegsHi = 192;
+    // (56 / 224 for the row-major one-slab configurations, 120 / 192 for the others; 88 / 208 and 72 / 216 run the
+    // sweep 17 % and 27 % slower: ptxas allocates the K loop differently at every split)
+    static constexpr bool kWideSplit = !TWO_CTA && !MN_MAJOR && SLABS == 1;
+    static constexpr int kRegsLo = kWideSplit ? 56 : 120, kRegsHi = kWideSplit ? 224 : 192;
 #endif
     static_assert(128 * kRegsLo + 256 * kRegsHi <= 64512 && kRegsLo % 8 == 0 && kRegsHi % 8 == 0, "register split");
     static_assert(kColsPerThread == 64 || kColsPerThread == 128, "epilogue handles 64 or 128 columns per thread");
