@@ -48,8 +48,8 @@ SWEEP = [(m, n, k) for m in (1024, 6144) for (n, k) in NK_PAIRS]
 # ncu pass (two DRAM counters, --clock-control none, caches flushed before each measured launch) over the fifth
 # sweep of `bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-extras`, taken with the kernel as it is now.
 # Reads = A + B + scales once; C mostly stays in the 126 MB L2 at kernel end, hence traffic < algorithmic.
-NCU_DRAM_BYTES = [18648576, 6402560, 11744000, 2166016, 16907520, 40677376, 19013376, 11282432, 2697984, 56920320,
-                  14554112, 49621248, 30287104, 60109567, 113781248, 65886208, 49148928, 5514240]
+NCU_DRAM_BYTES = [18649344, 6402816, 11740928, 2173440, 16908032, 40669696, 19015680, 11283712, 2697984, 57371392,
+                  14570240, 49792255, 30637824, 61002752, 116749312, 66869760, 49148928, 5439488]
 # same two counters for the largest moe_gemm_kernel launch of the single-GPU MoE layer (routed fc1)
 MOE_NCU_DRAM_BYTES = 2.91e9
 METRIC = "fp8_blockscaled_gemm_tflops"
