@@ -347,6 +347,32 @@ def test_reference_physical_layout_entry(rf_lib, m, n, k, seed):
     assert_close(c.view(torch.uint16).cpu().numpy(), o.fp8_gemm(a, b, a_s, b_s))
 
 
+def test_stream_k_plan_entry_is_a_plain_pass_where_stream_k_does_not_apply(rf_lib):
+    """A shape whose table entry says stream-K still runs through the reference-layout entry (MN-major operands
+    have no stream-K instantiation): the plan degrades to the plain pass, results unchanged."""
+    m, n, k = 1040, 3072, 1536
+    a, b, a_s, b_s = o.generate_input(m, n, k, 61, "randn")
+    from tests.helpers import to_dev
+    assert rf_lib.rf_fp8_gemm_set_plan(m, n, k, 256, -1) == 0
+    try:
+        assert rf_lib.rf_fp8_gemm_choose_split(m, n, k) == -1
+        exp = o.fp8_gemm(a, b, a_s, b_s)
+        # row-major entry: stream-K
+        assert_close(run_gemm(a, b, a_s, b_s), exp)
+        # reference layout: plain pass
+        da, db = to_dev(np.ascontiguousarray(a.T)), to_dev(np.ascontiguousarray(b.T))
+        das, dbs = to_dev(np.ascontiguousarray(a_s.T)), to_dev(np.ascontiguousarray(b_s.T))
+        full, c = canary_output(m, n)
+        st = rf_lib.rf_fp8_gemm_colmajor(da.data_ptr(), db.data_ptr(), das.data_ptr(), dbs.data_ptr(), c.data_ptr(),
+                                         m, n, k, None, 0, None)
+        assert st == 0
+        torch.cuda.synchronize()
+        assert G.device_status() == 0 and canary_intact(full, m, n)
+        assert_close(c.view(torch.uint16).cpu().numpy(), exp)
+    finally:
+        rf_lib.rf_fp8_gemm_set_plan(m, n, k, 0, 0)
+
+
 def test_reference_physical_layout_rejects_unaligned_m(rf_lib):
     a, b, a_s, b_s = o.generate_input(72, 64, 128, 1)
     from tests.helpers import to_dev
