@@ -523,7 +523,7 @@ def run_extras(args, rank, world, dev, dist, peaks):
     bias = torch.from_numpy(bias_np[order]).to(dev)
     layer = mg.ExpertParallelMoE(cfg, w, t_loc, dev, router_bias=bias, push_results=not args.ep_pull)
     if args.ep_dispatch_blocks:
-        layer.set_dispatch_blocks(args.ep_dispatch_blocks)
+        layer.set_dispatch_blocks(max(0, args.ep_dispatch_blocks))
     ms = _timed(lambda: layer.forward(x), 5, 2, dev, world, dist)
     layer.set_trace(True)
     y = layer.forward(x)
@@ -935,7 +935,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE and N-split GEMM workloads")
     ap.add_argument("--ep-dispatch-blocks", type=int, default=0,
-                    help="expert-parallel MoE: grid cap of the dispatch kernel (0 = library default)")
+                    help="expert-parallel MoE: SMs the dispatch owns (0 = library default: 32 on more than one GPU; "
+                         "-1 = none, the dispatch spreads over every SM)")
     ap.add_argument("--ep-pull", action="store_true",
                     help="expert-parallel MoE: combine pulls the expert outputs instead of fc2 pushing them")
     ap.add_argument("--workload", default="sweep", choices=["sweep", "moe", "multi"],

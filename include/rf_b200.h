@@ -472,8 +472,10 @@ int rf_moe_ep_set_weights(RfMoeEp *ep, const void *router_weight, const float *r
 int rf_moe_ep_forward(RfMoeEp *ep, const void *x, void *out, rf_stream_t stream);
 enum { RF_MOE_EP_OPT_TRACE = 1,            /* value != 0: record an event after every stage of forward   */
        RF_MOE_EP_OPT_DISPATCH_BLOCKS = 2   /* value = R in 1..64: the dispatch runs as R blocks that each own
-                                              an SM and the shared expert's GEMMs on the other SMs beside it
-                                              (0, the default: dispatch blocks on every SM, the two in turn)  */ };
+                                              an SM and move the rows with bulk copies (local HBM -> shared
+                                              memory -> the owner's receive buffer), the shared expert's GEMMs
+                                              on the other SMs beside them; 0: dispatch blocks on every SM, the
+                                              two in turn.  Default: 32 when world > 1, else 0.              */ };
 int rf_moe_ep_set_option(RfMoeEp *ep, int option, int value);
 /* Milliseconds of the stages of the last traced forward (synchronises); returns the number of stages.  */
 int rf_moe_ep_stage_times(RfMoeEp *ep, float *ms, const char **names, int max_stages);

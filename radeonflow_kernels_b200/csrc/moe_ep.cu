@@ -56,9 +56,8 @@ ep_layout_kernel(const int* __restrict__ counts_all, int rank, int world, int n_
 
 // One row per block iteration: the row's indices are read once (not once per 16 bytes), then the
 // block's threads move the row with up to four independent 16-byte loads in flight each before the
-// matching peer stores.  Launched either as many 256-thread blocks spread over every SM, or (SM partition) as
-// a few 1024-thread blocks that each claim a whole SM through their shared-memory request, so that a
-// persistent GEMM with a correspondingly smaller grid runs beside them on the remaining SMs.
+// matching peer stores.  Launched as many 256-thread blocks spread over every SM (the SM-partitioned dispatch is
+// ep_dispatch_bulk_kernel below).
 __global__ void __launch_bounds__(1024)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted_experts,
                    const int* __restrict__ permuted_rows, const int* __restrict__ first_token_offset,
@@ -111,6 +110,74 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted
             if (with_meta) static_cast<int*>(pick_peer(recv_meta, q))[row] = (rank << kEpMetaSlotBits) | p;
         }
     }
+}
+
+// The dispatch for the SM partition: a few blocks that own an SM each move the rows with the copy engine instead
+// of with loads and stores.  Each of a block's kEpBulkWarps warps owns one row buffer in shared memory and moves
+// one row at a time through it: a bulk load of the token row (local HBM -> shared memory, counted on the warp's
+// mbarrier), then a bulk store of the buffer into the owner's receive buffer (a peer GPU's memory: posted writes
+// over NVLink); the buffer is reloaded once that store has finished reading it.  What an SM keeps in flight is
+// bounded by its shared memory (12 rows of 14 KB), about 50 GB/s per SM: 16-24 blocks keep NVLink busy and leave
+// the other SMs to the shared expert's GEMMs running beside them.
+constexpr int kEpBulkWarps = 12;
+
+__global__ void __launch_bounds__(32 * kEpBulkWarps)
+ep_dispatch_bulk_kernel(const uint4* __restrict__ x, const int* __restrict__ permuted_experts,
+                        const int* __restrict__ permuted_rows, const int* __restrict__ first_token_offset,
+                        const int* __restrict__ send_base, int n_tokens, int n_pairs, int vec_per_row,
+                        int experts_per_rank, int rank, int world, int capacity, PeerPtrs recv_x, PeerPtrs recv_meta,
+                        int with_meta, int* __restrict__ pair_rank, int* __restrict__ pair_row,
+                        uint4* __restrict__ drop_fill, int* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t ep_smem[];
+    __shared__ __align__(8) unsigned long long bars[kEpBulkWarps];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row_bytes = (uint32_t)vec_per_row * 16u;
+    const uint32_t buf = smem_u32(ep_smem) + (uint32_t)warp * row_bytes;
+    const uint32_t bar = smem_u32(bars) + 8u * warp;
+    if (lane == 0) mbar_init(bar, 1);
+    mbar_fence_init();
+    __syncwarp();
+    const int p0 = __ldg(first_token_offset + ((rank + 1) % world) * experts_per_rank);
+    const int n_warps = gridDim.x * kEpBulkWarps;
+    uint32_t cnt = 0;                 // rows this warp has moved
+    for (int i = blockIdx.x * kEpBulkWarps + warp; i < n_pairs; i += n_warps) {
+        int p = i + p0;
+        if (p >= n_pairs) p -= n_pairs;
+        const int e = __ldg(permuted_experts + p);
+        const int q = e / experts_per_rank;
+        const int row = __ldg(send_base + e) + (p - __ldg(first_token_offset + e));
+        if (row >= capacity) {
+            // receive buffer full: dropped and reported, as in ep_dispatch_kernel
+            if (drop_fill != nullptr)
+                for (int v0 = lane; v0 < vec_per_row; v0 += 32)
+                    drop_fill[(size_t)p * vec_per_row + v0] = make_uint4(0u, 0u, 0u, 0u);
+            if (lane == 0) {
+                pair_rank[p] = -1;
+                pair_row[p] = 0;
+                atomicOr(status + kStatusDiagWord, (int)kDiagEpOverflow);
+            }
+            continue;
+        }
+        const int tok = __ldg(permuted_rows + p) % n_tokens;
+        if (lane == 0) {
+            tma_store_wait_read<0>();         // the previous row's store has finished reading the buffer
+            mbar_expect_tx(bar, row_bytes);
+            bulk_load(buf, x + (size_t)tok * vec_per_row, row_bytes, bar);
+            pair_rank[p] = q;
+            pair_row[p] = row;
+            if (with_meta) static_cast<int*>(pick_peer(recv_meta, q))[row] = (rank << kEpMetaSlotBits) | p;
+        }
+        __syncwarp();
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, cnt & 1u, status, kErrSchedWait, 0));
+        if (!ok) break;
+        if (lane == 0) {
+            bulk_store(static_cast<uint4*>(pick_peer(recv_x, q)) + (size_t)row * vec_per_row, buf, row_bytes);
+            tma_store_commit();
+        }
+        ++cnt;
+    }
+    // the rows must have landed before the kernel (and the rendezvous that follows it) completes
+    if (lane == 0) tma_store_wait_all<0>();
 }
 
 __global__ void __launch_bounds__(256)
@@ -255,25 +322,28 @@ cudaError_t moe_ep_dispatch_launch(const void* x, const int* permuted_experts, c
     const int vec = row_bytes / 16;
     if (n_pairs == 0) return cudaSuccess;
     if (max_blocks > 0) {
-        // SM partition: `max_blocks` blocks of 1024 threads, each asking for most of an SM's shared memory so that
-        // no second block (and no CTA of the GEMM running beside it) shares its SM.  A block is four groups of 256
-        // threads, each moving a row at a time: four rows' worth of loads (64 KB) are in flight per SM.
-        constexpr int kOwnSmBytes = 160 * 1024;
-        static bool attr_set[64] = {};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev < 64 && !attr_set[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(ep_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 kOwnSmBytes);
-            if (e != cudaSuccess) return e;
-            attr_set[dev] = true;
+        // SM partition.  Rows of which twelve fit an SM's shared memory travel by bulk copies:
+        const size_t ring_bytes = (size_t)kEpBulkWarps * row_bytes;
+        if (row_bytes % 16 == 0 && ring_bytes <= 200 * 1024) {
+            // ask for at least 120 KB so that no CTA of the GEMM running beside the dispatch shares the SM
+            const size_t smem = ring_bytes > 120 * 1024 ? ring_bytes : 120 * 1024;
+            static bool bulk_attr_set[64] = {};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (dev < 64 && !bulk_attr_set[dev]) {
+                cudaError_t e = cudaFuncSetAttribute(ep_dispatch_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     200 * 1024);
+                if (e != cudaSuccess) return e;
+                bulk_attr_set[dev] = true;
+            }
+            int blocks = max_blocks * kEpBulkWarps < n_pairs ? max_blocks : (n_pairs + kEpBulkWarps - 1) / kEpBulkWarps;
+            ep_dispatch_bulk_kernel<<<(unsigned)blocks, 32 * kEpBulkWarps, smem, stream>>>(
+                static_cast<const uint4*>(x), permuted_experts, permuted_rows, first_token_offset, send_base, n_tokens,
+                n_pairs, vec, experts_per_rank, rank, world, capacity, recv_x, recv_meta ? *recv_meta : recv_x,
+                recv_meta ? 1 : 0, pair_rank, pair_row, static_cast<uint4*>(drop_fill), status);
+            return cudaGetLastError();
         }
-        int blocks = max_blocks * 4 < n_pairs ? max_blocks : (n_pairs + 3) / 4;
-        ep_dispatch_kernel<<<(unsigned)blocks, 1024, kOwnSmBytes, stream>>>(
-            static_cast<const uint4*>(x), permuted_experts, permuted_rows, first_token_offset, send_base, n_tokens,
-            n_pairs, vec, experts_per_rank, rank, world, capacity, recv_x, recv_meta ? *recv_meta : recv_x,
-            recv_meta ? 1 : 0, pair_rank, pair_row, static_cast<uint4*>(drop_fill), status);
-        return cudaGetLastError();
+        // (longer rows: no partition; the dispatch below spreads over every SM)
     }
     int blocks = num_sms * 8;
     if (blocks > n_pairs) blocks = n_pairs;
