@@ -935,7 +935,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE and N-split GEMM workloads")
     ap.add_argument("--ep-dispatch-blocks", type=int, default=0,
-                    help="expert-parallel MoE: SMs the dispatch owns (0 = library default: 32 on more than one GPU; "
+                    help="expert-parallel MoE: SMs the dispatch owns (0 = library default: 32 on 2 to 4 GPUs; "
                          "-1 = none, the dispatch spreads over every SM)")
     ap.add_argument("--ep-pull", action="store_true",
                     help="expert-parallel MoE: combine pulls the expert outputs instead of fc2 pushing them")

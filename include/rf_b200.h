@@ -475,7 +475,7 @@ enum { RF_MOE_EP_OPT_TRACE = 1,            /* value != 0: record an event after 
                                               an SM and move the rows with bulk copies (local HBM -> shared
                                               memory -> the owner's receive buffer), the shared expert's GEMMs
                                               on the other SMs beside them; 0: dispatch blocks on every SM, the
-                                              two in turn.  Default: 32 when world > 1, else 0.              */ };
+                                              two in turn.  Default: 32 on 2 to 4 GPUs, else 0.             */ };
 int rf_moe_ep_set_option(RfMoeEp *ep, int option, int value);
 /* Milliseconds of the stages of the last traced forward (synchronises); returns the number of stages.  */
 int rf_moe_ep_stage_times(RfMoeEp *ep, float *ms, const char **names, int max_stages);

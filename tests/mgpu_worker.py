@@ -97,7 +97,7 @@ def main():
     assert np.array_equal(layer.send_base.cpu().numpy(), sb)
     assert np.array_equal(layer.recv_offsets.cpu().numpy(), ro)
     assert layer.received_rows() == int(counts_all[:, rank * e_loc:(rank + 1) * e_loc].sum())
-    # SM partition (the default on more than one GPU): the dispatch as a few blocks that own an SM each and move the
+    # SM partition (the default on 2 to 4 GPUs): the dispatch as a few blocks that own an SM each and move the
     # rows with bulk copies, the shared expert's GEMMs beside them on the remaining SMs; and the dispatch spread
     # over every SM (the default on one GPU) - same result, bit for bit
     for blocks in (8, 0):
@@ -106,7 +106,7 @@ def main():
         torch.cuda.synchronize()
         assert G.device_status() == 0
         assert torch.equal(out_part, out_pull), f"dispatch with {blocks} blocks of its own changed the result"
-    layer.set_dispatch_blocks(32 if world > 1 else 0)
+    layer.set_dispatch_blocks(32 if 1 < world <= 4 else 0)
     layer.close()
 
     # ---- 3. receive buffers smaller than the traffic: rows beyond the capacity are dropped and reported,
